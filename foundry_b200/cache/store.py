@@ -30,6 +30,7 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None  # None: every earlier position stays readable
+    v_head_dim: Optional[int] = None  # None: values have the keys' size
 
 
 @dataclass(frozen=True)
@@ -48,9 +49,18 @@ class KVGroup:
         self.entries = entries
         self.index_of = {e: i for i, e in enumerate(entries)}
         self.pages = GroupPages(page_count, request.window)
-        self.storage = torch.zeros(
-            (len(entries), page_count, 2, request.kv_heads, PAGE, request.head_dim),
-            dtype=dtype, device=device)
+        self.v_storage = None
+        if request.v_head_dim in (None, request.head_dim):
+            self.storage = torch.zeros(
+                (len(entries), page_count, 2, request.kv_heads, PAGE, request.head_dim),
+                dtype=dtype, device=device)
+        else:  # values of another size than keys: two storages with the same paging
+            self.storage = torch.zeros(
+                (len(entries), page_count, request.kv_heads, PAGE, request.head_dim),
+                dtype=dtype, device=device)
+            self.v_storage = torch.zeros(
+                (len(entries), page_count, request.kv_heads, PAGE, request.v_head_dim),
+                dtype=dtype, device=device)
         self._views: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
 
     @property
@@ -65,12 +75,16 @@ class KVGroup:
         views = self._views.get(entry)
         if views is None:  # the views never change: made once per entry
             block = self.storage[self.index_of[entry]]
-            views = self._views[entry] = (block[:, 0], block[:, 1])
+            if self.v_storage is None:
+                views = self._views[entry] = (block[:, 0], block[:, 1])
+            else:
+                views = self._views[entry] = (block, self.v_storage[self.index_of[entry]])
         return views
 
     def bytes_per_token(self) -> int:
         r = self.request
-        return len(self.entries) * 2 * r.kv_heads * r.head_dim * self.storage.element_size()
+        return (len(self.entries) * r.kv_heads * (r.head_dim + (r.v_head_dim or r.head_dim))
+                * self.storage.element_size())
 
 
 @dataclass

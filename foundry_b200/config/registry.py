@@ -9,7 +9,7 @@ single module. Here config.json's `architectures[0]` (falling back to
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Mapping
+from typing import Any, Callable, Dict, List, Mapping, Optional
 
 from . import errors
 from .spec import ModelSpec
@@ -21,6 +21,9 @@ class Architecture:
     model_type: str  # config.json `model_type`
     parse_config: Callable[[Mapping[str, Any]], Any]  # decoded json -> typed config
     build_spec: Callable[[Any], ModelSpec]  # typed config -> description of the model
+    # (typed config, opened weight files) -> typed config: for sizes that only the
+    # tensors' shapes give; None when config.json gives them all
+    complete_from_files: Optional[Callable[[Any, Any], Any]] = None
 
 
 _BY_NAME: Dict[str, Architecture] = {}
@@ -45,6 +48,8 @@ def resolve_architecture(doc: Mapping[str, Any]) -> Architecture:
     """Pick the architecture a decoded config.json names."""
     import foundry_b200.models  # noqa: F401  (registers the built-in architectures)
     archs = doc.get("architectures")
+    if archs is None and isinstance(doc.get("architecture"), str):
+        archs = [doc["architecture"]]  # some designs name themselves with a single string
     if isinstance(archs, list):
         for name in archs:
             if name in _BY_NAME:

@@ -36,13 +36,16 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]  # None: the layer has no feed-forward (blocks that allow it)
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
     # tensor-name component of each part under `prefix`, e.g. mixer -> "self_attn"
     names: Mapping[str, str] = field(default_factory=lambda: {
         "mixer": "mixer", "feed_forward": "feed_forward",
         "mixer_norm": "mixer_norm", "feed_forward_norm": "feed_forward_norm"})
+    # norms of a part's OUTPUT, for blocks that normalise on both sides of a part
+    mixer_post_norm: Optional[PartSpec] = None
+    feed_forward_post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -58,6 +61,9 @@ class ScheduleEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    # (index into `ModelSpec.junctions`, number of the pass): a part that rewrites
+    # the residual stream right before this run (see parts/junction.py)
+    junction: Optional[Tuple[int, int]] = None
 
 
 @dataclass(frozen=True)
@@ -74,6 +80,9 @@ class ModelSpec:
     output_head_name: Optional[str]  # None: the output head is the embedding table
     eos_token_ids: Tuple[int, ...] = ()
     ignorable_tensors: Tuple[str, ...] = ()  # fnmatch patterns that may be present unused
+    embedding: Optional[PartSpec] = None  # None: the plain table lookup
+    junctions: Tuple[PartSpec, ...] = ()
+    junction_prefixes: Tuple[str, ...] = ()  # tensor-name prefix of each junction
 
     def cache_entry_count(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)
@@ -84,6 +93,9 @@ class ModelSpec:
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule[{position}] names layer {entry.layer}, "
                                  f"the model has {len(self.layers)}")
+            if entry.junction is not None and not 0 <= entry.junction[0] < len(self.junctions):
+                raise ValueError(f"schedule[{position}] names junction {entry.junction[0]}, "
+                                 f"the model has {len(self.junctions)}")
             if entry.cache < 0:
                 raise ValueError(f"schedule[{position}] names cache entry {entry.cache}")
             if entry.writes_cache:

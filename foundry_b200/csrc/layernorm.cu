@@ -1,0 +1,178 @@
+// Layer normalisation with weight and bias, fused with the residual sum on
+// either side of it, and the embedding with a sinusoidal position vector.
+//
+//   LN(x) = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w + b
+//
+// A block that normalises a part's input AND its output ("sandwich") does, per
+// token row, between two parts:
+//
+//   resid += LN_post(y)          y: the output of the part that just ran
+//   h      = LN_pre(resid)       h: the input of the part that runs next
+//
+// `fb_ln_add_ln` makes both in one pass over the row; either half may be absent
+// (the first norm of a model has no y, the last sum no h). Statistics, the sum
+// and the residual are 32-bit; the variance is the mean of squared deviations
+// taken in a second pass over the row held in shared memory.
+#include "common.cuh"
+
+namespace {
+
+template <typename TY, typename TO>
+__global__ void ln_add_ln_kernel(const TY* y, const float* __restrict__ w1,
+                                 const float* __restrict__ b1, float* resid,
+                                 const float* __restrict__ w2, const float* __restrict__ b2,
+                                 TO* __restrict__ out, int W, float eps, float inv_w) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  extern __shared__ float row[];  // W floats
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * W;
+  float* x = resid + base;
+  if (y != nullptr && w1 == nullptr) {  // a plain sum: y joins the residual as it is
+    const TY* yr = y + base;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = x[i] + fb_load_coherent<TY>(yr + i);
+      x[i] = v;
+      row[i] = v;
+    }
+  } else if (y != nullptr) {
+    const TY* yr = y + base;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = fb_load_coherent<TY>(yr + i);
+      row[i] = v;
+      s += v;
+    }
+    const float mean = fb_block_sum(s, scratch) * inv_w;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float d = row[i] - mean;
+      q += d * d;
+    }
+    const float r = 1.0f / sqrtf(fb_block_sum(q, scratch) * inv_w + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = x[i] + ((row[i] - mean) * r * w1[i] + b1[i]);
+      x[i] = v;
+      row[i] = v;
+    }
+  } else if (out != nullptr) {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = x[i];
+  }
+  if (out == nullptr) return;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
+  const float mean = fb_block_sum(s, scratch) * inv_w;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float d = row[i] - mean;
+    q += d * d;
+  }
+  const float r = 1.0f / sqrtf(fb_block_sum(q, scratch) * inv_w + eps);
+  TO* o = out + base;
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    o[i] = fb_from_float<TO>((row[i] - mean) * r * w2[i] + b2[i]);
+}
+
+// x[t, :] = table[ids[t], :] * scale + pe(positions[t]), pe[2i] = sin(p f_i),
+// pe[2i+1] = cos(p f_i). The angle is the double-precision product of the
+// position and a double-precision frequency, so that it is exact to 32 bits
+// at any position; `copy`, when given, receives the same rows.
+template <typename T>
+__global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                      const int* __restrict__ positions,
+                                      const double* __restrict__ freq, float scale,
+                                      float* __restrict__ out, float* __restrict__ copy, int W,
+                                      int V) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const double p = (double)positions[t];
+  const bool inside = id >= 0 && id < V;
+  const T* src = table + (size_t)(inside ? id : 0) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const double angle = p * freq[i >> 1];
+    const float pe = (float)((i & 1) ? cos(angle) : sin(angle));
+    const float e = inside ? fb_to_float<T>(src[i]) * scale : 0.f;
+    const float v = e + pe;
+    out[(size_t)t * W + i] = v;
+    if (copy != nullptr) copy[(size_t)t * W + i] = v;
+  }
+}
+
+// out[t, :W] = resid[t, :] (+ nothing), out[t, W:] = x0[t, :], rounded to the
+// activation type: the input rows of a product over two streams side by side.
+template <typename TO>
+__global__ void concat_cast_kernel(const float* a, const float* b, TO* __restrict__ out, int W) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    out[t * 2 * W + i] = fb_from_float<TO>(__ldcg(a + t * W + i));
+    out[t * 2 * W + W + i] = fb_from_float<TO>(__ldcg(b + t * W + i));
+  }
+}
+
+// x[t, :] += v[:]
+__global__ void add_row_vector_kernel(float* x, const float* __restrict__ v, int W) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) x[t * W + i] += v[i];
+}
+}  // namespace
+
+FB_API int fb_ln_add_ln(const void* y, int y_dtype, const float* w1, const float* b1, float* resid,
+                        const float* w2, const float* b2, void* out, int out_dtype, int T, int W,
+                        float eps, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && W > 0 && eps > 0.f, "ln_add_ln: bad sizes T=%d W=%d", T, W);
+  FB_REQUIRE(resid != nullptr, "ln_add_ln: no residual rows");
+  FB_REQUIRE(y == nullptr || ((w1 != nullptr) == (b1 != nullptr)),
+             "ln_add_ln: the norm of y has a weight or a bias but not both");
+  FB_REQUIRE(out == nullptr || (w2 && b2), "ln_add_ln: the norm of the sum has no weight or bias");
+  FB_REQUIRE((size_t)W * 4 <= 200 * 1024, "ln_add_ln: rows of %d do not fit shared memory", W);
+  if (T == 0 || (y == nullptr && out == nullptr)) return 0;
+  const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+  const size_t smem = (size_t)W * 4;
+#define FB_LN_LAUNCH(TY, TO)                                                                   \
+  do {                                                                                         \
+    static bool seen[64];                                                                      \
+    if (smem > 48 * 1024 && fb_first_use_on_device(seen))                                      \
+      cudaFuncSetAttribute(ln_add_ln_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           200 * 1024);                                                        \
+    fb_launch(ln_add_ln_kernel<TY, TO>, dim3(T), dim3(threads), smem, stream, (const TY*)y, w1, \
+              b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W);                           \
+  } while (0)
+  const int yd = y ? y_dtype : FB_F32, od = out ? out_dtype : FB_F32;
+  FB_DISPATCH_DTYPE(yd, TY, FB_DISPATCH_DTYPE(od, TO, FB_LN_LAUNCH(TY, TO)));
+#undef FB_LN_LAUNCH
+  return fb_check_launch("ln_add_ln");
+}
+
+FB_API int fb_embed_sinusoid(const void* table, int table_dtype, const int* ids,
+                             const int* positions, const double* freq, float scale, float* out,
+                             float* copy, int T, int W, int V, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && W > 0 && W % 2 == 0 && V > 0, "embed_sinusoid: bad sizes T=%d W=%d V=%d", T,
+             W, V);
+  if (T == 0) return 0;
+  const int threads = W >= 1024 ? 256 : 128;
+  FB_DISPATCH_DTYPE(table_dtype, E, (fb_launch(embed_sinusoid_kernel<E>, dim3(T), dim3(threads), 0,
+      stream, (const E*)table, ids, positions, freq, scale, out, copy, W, V)));
+  return fb_check_launch("embed_sinusoid");
+}
+
+FB_API int fb_concat_cast(const float* a, const float* b, void* out, int out_dtype, int T, int W,
+                          cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && W > 0, "concat_cast: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return 0;
+  FB_DISPATCH_DTYPE(out_dtype, E, (fb_launch(concat_cast_kernel<E>, dim3(T), dim3(256), 0, stream,
+      a, b, (E*)out, W)));
+  return fb_check_launch("concat_cast");
+}
+
+FB_API int fb_add_row_vector(float* x, const float* v, int T, int W, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && W > 0, "add_row_vector: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return 0;
+  fb_launch(add_row_vector_kernel, dim3(T), dim3(256), 0, stream, x, v, W);
+  return fb_check_launch("add_row_vector");
+}

@@ -1,0 +1,389 @@
+// Mixers that carry a state of fixed size from token to token: the pieces
+// around two linear recurrences over a per-head matrix state S [dim, vdim].
+//
+// Gated delta rule with a decay per key channel (one step, per head):
+//   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+// RWKV-style time mixing with a bonus for the current token (per head):
+//   o = (S + diag(b) k v^T)^T r;  S <- diag(w) S + k v^T
+//
+// Both recurrences act on the columns of S independently, so a thread owns a
+// slice of one column in registers (16 rows at most, the key rows dealt out
+// over KP lanes) and columns are spread over lanes, warps and blocks. A step
+// is two dot products over the key rows, finished by shuffles among the KP
+// lanes of a column. The state is 32-bit and lives in the sequence's state row
+// between steps; every sequence of the step is walked by its own blocks from
+// `cu_tokens`, so a step may bring any number of tokens per sequence.
+//
+// Around them, per token: the mix with the previous token's input (token
+// shift), a short causal convolution with SiLU and unit-length heads, the
+// decays, and the per-head RMS norm with an output gate. The inputs that these
+// need from before the step (the previous token's row, the convolution's last
+// taps - 1 inputs) are part of the state row too, written by
+// `fb_state_tail_update` after their readers have run.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------- token shift
+// out[m, t, :] = h[t] + (h[t-1] - h[t]) * mu[m], h[t-1] being the state's row
+// for the first token that a sequence brings in this step.
+template <typename T>
+__global__ void token_shift_mix_kernel(const T* h, const float* state, long long state_stride,
+                                       long long prev_offset, const float* __restrict__ mu,
+                                       T* __restrict__ out, const int* __restrict__ seq_of_token,
+                                       const int* __restrict__ cu_tokens,
+                                       const int* __restrict__ slots, int T_, int W, int n_mix) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int t = blockIdx.x;
+  const int seq = seq_of_token[t];
+  if (seq < 0) {
+    for (int m = 0; m < n_mix; ++m)
+      for (int i = threadIdx.x; i < W; i += blockDim.x)
+        out[((size_t)m * T_ + t) * W + i] = fb_from_float<T>(0.f);
+    return;
+  }
+  const bool first = t == cu_tokens[seq];
+  const float* prev_state = state + (long long)slots[seq] * state_stride + prev_offset;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float x = fb_load_coherent<T>(h + (size_t)t * W + i);
+    const float p = first ? __ldcg(prev_state + i) : fb_load_coherent<T>(h + (size_t)(t - 1) * W + i);
+    const float d = p - x;
+    for (int m = 0; m < n_mix; ++m)
+      out[((size_t)m * T_ + t) * W + i] = fb_from_float<T>(x + d * mu[(size_t)m * W + i]);
+  }
+}
+
+// ------------------------------------------------------- tail of the inputs
+// state tail [n_tail, C] <- the last n_tail rows of (old tail ++ this step's rows).
+template <typename T>
+__global__ void state_tail_update_kernel(const T* x, long long ld, float* state,
+                                         long long state_stride, long long offset, int n_tail,
+                                         int C, const int* __restrict__ cu_tokens,
+                                         const int* __restrict__ slots) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int seq = blockIdx.x;
+  const int start = cu_tokens[seq], n = cu_tokens[seq + 1] - start;
+  if (n <= 0) return;
+  float* tail = state + (long long)slots[seq] * state_stride + offset;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    for (int r = 0; r < n_tail; ++r) {
+      const int src = n + r;  // index into old tail (n_tail rows) followed by the step's rows
+      const float v = src < n_tail ? tail[(size_t)src * C + c]
+                                   : fb_load_coherent<T>(x + (size_t)(start + src - n_tail) * ld + c);
+      tail[(size_t)r * C + c] = v;  // row r is read by no later iteration (src > r)
+    }
+  }
+}
+
+// ------------------------------------- causal convolution + SiLU + unit heads
+// y[t, c] = silu(sum_a w[c, a] x[t - (taps - 1 - a), c]); rows in front of the
+// step come from the state's tail, which holds zeros at a sequence's start.
+// Then the first `n_unit` heads of `dim` channels are scaled to unit length,
+// x / sqrt(sum(x^2) + unit_eps), the first `n_scaled` of them also by `extra`.
+__global__ void conv_silu_unit_kernel(const float* x, long long ld, const float* __restrict__ w,
+                                      int taps, const float* state, long long state_stride,
+                                      long long tail_offset, float* __restrict__ out, int C,
+                                      const int* __restrict__ seq_of_token,
+                                      const int* __restrict__ cu_tokens,
+                                      const int* __restrict__ slots, int n_unit, int dim,
+                                      int n_scaled, float extra, float unit_eps) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  extern __shared__ float y[];  // C floats
+  const int t = blockIdx.x;
+  const int seq = seq_of_token[t];
+  if (seq < 0) {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) out[(size_t)t * C + c] = 0.f;
+    return;
+  }
+  const int start = cu_tokens[seq];
+  const int n_tail = taps - 1;
+  const float* tail = state + (long long)slots[seq] * state_stride + tail_offset;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int a = 0; a < taps; ++a) {
+      const int idx = t - (taps - 1 - a) - start;  // row of the step, negative: the tail
+      const float v = idx >= 0 ? __ldcg(x + (size_t)(start + idx) * ld + c)
+                               : __ldcg(tail + (size_t)(n_tail + idx) * C + c);
+      acc = fmaf(w[(size_t)c * taps + a], v, acc);
+    }
+    y[c] = acc * sigmoidf_(acc);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int head = warp; head < n_unit; head += nwarps) {
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) ss += y[head * dim + d] * y[head * dim + d];
+    ss = fb_warp_sum(ss);
+    const float r = (head < n_scaled ? extra : 1.0f) / sqrtf(ss + unit_eps);
+    for (int d = lane; d < dim; d += 32) y[head * dim + d] *= r;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) out[(size_t)t * C + c] = y[c];
+}
+
+// -------------------------------------------------------------------- decays
+// mode 0: x <- exp(-exp(A[head]) * softplus(x + bias[c]))   (c = head * per_head + channel)
+// mode 1: x <- exp(-exp(x + bias[c]))
+__global__ void decay_gate_kernel(float* x, long long n_total, int n, int per_head,
+                                  const float* __restrict__ A, const float* __restrict__ bias,
+                                  int mode) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % n);
+    const float v = x[i] + bias[c];
+    x[i] = mode == 0 ? expf(-expf(A[c / per_head]) * softplusf_(v)) : expf(-expf(v));
+  }
+}
+
+// ------------------------------------------------------------ the recurrences
+constexpr int R = 16;  // state rows a thread holds
+
+struct ScanArgs {
+  const float* q; long long q_ld;   // [T, *]: query (delta) or receptance (wkv); head h at (h / rep) * dim
+  const float* k; long long k_ld;   // keys, same head mapping
+  const float* v; long long v_ld;   // values: head h at h * vdim
+  const float* g; long long g_ld;   // decays: head h at h * dim
+  const float* beta; long long beta_ld;  // delta: raw step size per head (sigmoid applied here)
+  const float* bonus;               // wkv: [H, dim]
+  float* state; long long state_stride; long long s_offset;
+  float* out;                       // [T, H * vdim]
+  const int* cu_tokens; const int* slots;
+  int H, rep, dim, vdim;
+};
+
+template <int MODE, int KP>
+__global__ void __launch_bounds__(256) scan_kernel(ScanArgs a) {
+  fb_pdl_wait();
+  constexpr int COLS_W = 32 / KP;  // columns a warp holds
+  const int seq = blockIdx.x, h = blockIdx.y;
+  const int start = a.cu_tokens[seq], n = a.cu_tokens[seq + 1] - start;
+  if (n <= 0) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int part = lane / COLS_W;
+  const int j = (blockIdx.z * nwarps + warp) * COLS_W + lane % COLS_W;
+  const bool col = j < a.vdim;
+  const int dim = a.dim, vdim = a.vdim;
+  float* S = a.state + (long long)a.slots[seq] * a.state_stride + a.s_offset +
+             (long long)h * dim * vdim;
+  const long long qoff = (long long)(h / a.rep) * dim, goff = (long long)h * dim;
+
+  float s[R], bonus[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int row = i * KP + part;
+    s[i] = (col && row < dim) ? S[(size_t)row * vdim + j] : 0.f;
+    bonus[i] = (MODE == 1 && row < dim) ? a.bonus[goff + row] : 0.f;
+  }
+  float qn[R], kn[R], gn[R], vn = 0.f, bn = 0.f;
+  auto load = [&](int t) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int row = i * KP + part;
+      const bool ok = row < dim;
+      qn[i] = ok ? __ldcg(a.q + (size_t)t * a.q_ld + qoff + row) : 0.f;
+      kn[i] = ok ? __ldcg(a.k + (size_t)t * a.k_ld + qoff + row) : 0.f;
+      gn[i] = ok ? __ldcg(a.g + (size_t)t * a.g_ld + goff + row) : 0.f;
+    }
+    vn = col ? __ldcg(a.v + (size_t)t * a.v_ld + (size_t)h * vdim + j) : 0.f;
+    if (MODE == 0) bn = __ldcg(a.beta + (size_t)t * a.beta_ld + h);
+  };
+  load(start);
+  for (int t = start; t < start + n; ++t) {
+    float q[R], k[R], g[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) { q[i] = qn[i]; k[i] = kn[i]; g[i] = gn[i]; }
+    const float v = vn, braw = bn;
+    if (t + 1 < start + n) load(t + 1);  // the next token's loads fly while this one is worked
+    float o = 0.f;
+    if (MODE == 0) {
+      float kv = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        s[i] *= g[i];
+        kv = fmaf(s[i], k[i], kv);
+      }
+#pragma unroll
+      for (int off = COLS_W; off < 32; off <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
+      const float u = sigmoidf_(braw) * (v - kv);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        s[i] = fmaf(k[i], u, s[i]);
+        o = fmaf(s[i], q[i], o);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const float kvi = k[i] * v;
+        o = fmaf(q[i], fmaf(bonus[i], kvi, s[i]), o);
+        s[i] = fmaf(g[i], s[i], kvi);
+      }
+    }
+#pragma unroll
+    for (int off = COLS_W; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+    if (col && part == 0) a.out[(size_t)t * a.H * vdim + (size_t)h * vdim + j] = o;
+  }
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int row = i * KP + part;
+    if (col && row < dim) S[(size_t)row * vdim + j] = s[i];
+  }
+}
+
+// ------------------------------------------------- per-head RMS norm and gate
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[h * w_stride + :] * act(gate[t, h, :])
+// act: 0 sigmoid, 1 SiLU.
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ w, int w_stride,
+                                      const float* gate, long long gate_ld, int act, float eps,
+                                      T* __restrict__ out, int H, int vdim) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < H; h += nwarps) {
+    const float* row = o + ((size_t)t * H + h) * vdim;
+    float ss = 0.f;
+    for (int d = lane; d < vdim; d += 32) {
+      const float v = __ldcg(row + d);
+      ss += v * v;
+    }
+    const float r = 1.0f / sqrtf(fb_warp_sum(ss) / (float)vdim + eps);
+    for (int d = lane; d < vdim; d += 32) {
+      const float gz = __ldcg(gate + (size_t)t * gate_ld + (size_t)h * vdim + d);
+      const float ga = act == 0 ? sigmoidf_(gz) : gz * sigmoidf_(gz);
+      out[((size_t)t * H + h) * vdim + d] =
+          fb_from_float<T>(__ldcg(row + d) * r * w[(size_t)h * w_stride + d] * ga);
+    }
+  }
+}
+
+// out = act(in) rounded to the activation type; act: 0 identity, 1 tanh
+template <typename T>
+__global__ void unary_cast_kernel(const float* in, long long ld, T* __restrict__ out, int n,
+                                  int act) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = __ldcg(in + t * ld + i);
+    out[t * n + i] = fb_from_float<T>(act == 1 ? tanhf(v) : v);
+  }
+}
+}  // namespace
+
+FB_API int fb_token_shift_mix(const void* h, int dtype, const float* state, long long state_stride,
+                              long long prev_offset, const float* mu, void* out,
+                              const int* seq_of_token, const int* cu_tokens, const int* slots,
+                              int T, int W, int n_mix, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && W > 0 && n_mix > 0, "token_shift_mix: bad sizes");
+  if (T == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(token_shift_mix_kernel<E>, dim3(T), dim3(256), 0, stream,
+      (const E*)h, state, state_stride, prev_offset, mu, (E*)out, seq_of_token, cu_tokens, slots,
+      T, W, n_mix)));
+  return fb_check_launch("token_shift_mix");
+}
+
+FB_API int fb_state_tail_update(const void* x, int dtype, long long ld, float* state,
+                                long long state_stride, long long offset, int n_tail, int C,
+                                const int* cu_tokens, const int* slots, int n_seqs,
+                                cudaStream_t stream) {
+  FB_REQUIRE(n_seqs >= 0 && C > 0 && n_tail >= 0 && ld >= C, "state_tail_update: bad sizes");
+  if (n_seqs == 0 || n_tail == 0) return 0;
+  dim3 grid(n_seqs, (C + 255) / 256 < 64 ? (C + 255) / 256 : 64);
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(state_tail_update_kernel<E>, dim3(grid), dim3(256), 0,
+      stream, (const E*)x, ld, state, state_stride, offset, n_tail, C, cu_tokens, slots)));
+  return fb_check_launch("state_tail_update");
+}
+
+FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, int taps,
+                             const float* state, long long state_stride, long long tail_offset,
+                             float* out, int C, const int* seq_of_token, const int* cu_tokens,
+                             const int* slots, int n_unit, int dim, int n_scaled, float extra,
+                             float unit_eps, int T, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && C > 0 && taps >= 1 && ld >= C, "conv_silu_unit: bad sizes");
+  FB_REQUIRE(n_unit >= 0 && (long long)n_unit * dim <= C && n_scaled <= n_unit,
+             "conv_silu_unit: %d unit heads of %d exceed %d channels", n_unit, dim, C);
+  FB_REQUIRE((size_t)C * 4 <= 200 * 1024, "conv_silu_unit: %d channels do not fit shared memory", C);
+  if (T == 0) return 0;
+  const size_t smem = (size_t)C * 4;
+  static bool seen[64];
+  if (smem > 48 * 1024 && fb_first_use_on_device(seen))
+    cudaFuncSetAttribute(conv_silu_unit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+  fb_launch(conv_silu_unit_kernel, dim3(T), dim3(256), smem, stream, x, ld, w, taps, state,
+            state_stride, tail_offset, out, C, seq_of_token, cu_tokens, slots, n_unit, dim,
+            n_scaled, extra, unit_eps);
+  return fb_check_launch("conv_silu_unit");
+}
+
+FB_API int fb_decay_gate(float* x, int T, int n, int per_head, const float* A, const float* bias,
+                         int mode, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && n > 0 && per_head > 0 && bias != nullptr && (mode == 1 || A != nullptr),
+             "decay_gate: bad arguments");
+  if (T == 0) return 0;
+  const long long total = (long long)T * n;
+  const int blocks = (int)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048);
+  fb_launch(decay_gate_kernel, dim3(blocks), dim3(256), 0, stream, x, total, n, per_head, A, bias,
+            mode);
+  return fb_check_launch("decay_gate");
+}
+
+FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* k, long long k_ld,
+                         const float* v, long long v_ld, const float* g, long long g_ld,
+                         const float* beta, long long beta_ld, const float* bonus, float* state,
+                         long long state_stride, long long s_offset, float* out,
+                         const int* cu_tokens, const int* slots, int n_seqs, int H, int rep,
+                         int dim, int vdim, cudaStream_t stream) {
+  FB_REQUIRE(mode == 0 || mode == 1, "state_scan: unknown recurrence %d", mode);
+  FB_REQUIRE(n_seqs >= 0 && H > 0 && rep > 0 && H % rep == 0 && dim > 0 && vdim > 0,
+             "state_scan: bad sizes");
+  FB_REQUIRE(dim <= R * 32, "state_scan: %d key channels exceed %d", dim, R * 32);
+  FB_REQUIRE(mode == 0 ? beta != nullptr : bonus != nullptr, "state_scan: a missing input");
+  if (n_seqs == 0) return 0;
+  ScanArgs a{q, q_ld, k, k_ld, v, v_ld, g, g_ld, beta, beta_ld, bonus, state, state_stride,
+             s_offset, out, cu_tokens, slots, H, rep, dim, vdim};
+  int kp = 1;
+  while (kp * R < dim) kp *= 2;
+  const int cols_w = 32 / kp;
+  const int warps_needed = (vdim + cols_w - 1) / cols_w;
+  const int warps = warps_needed < 4 ? warps_needed : 4;
+  dim3 grid(n_seqs, H, (warps_needed + warps - 1) / warps);
+#define FB_SCAN(KP)                                                                              \
+  case KP:                                                                                       \
+    if (mode == 0) fb_launch(scan_kernel<0, KP>, grid, dim3(warps * 32), 0, stream, a);          \
+    else fb_launch(scan_kernel<1, KP>, grid, dim3(warps * 32), 0, stream, a);                    \
+    break;
+  switch (kp) {
+    FB_SCAN(1) FB_SCAN(2) FB_SCAN(4) FB_SCAN(8) FB_SCAN(16) FB_SCAN(32)
+    default: return fb_fail(1, "state_scan: no kernel for %d lanes a column", kp);
+  }
+#undef FB_SCAN
+  return fb_check_launch("state_scan");
+}
+
+FB_API int fb_head_norm_gate(const float* o, const float* w, int w_stride, const float* gate,
+                             long long gate_ld, int act, float eps, void* out, int dtype, int T,
+                             int H, int vdim, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && H > 0 && vdim > 0 && (act == 0 || act == 1), "head_norm_gate: bad sizes");
+  if (T == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(head_norm_gate_kernel<E>, dim3(T), dim3(256), 0, stream,
+      o, w, w_stride, gate, gate_ld, act, eps, (E*)out, H, vdim)));
+  return fb_check_launch("head_norm_gate");
+}
+
+FB_API int fb_unary_cast(const float* in, long long ld, void* out, int dtype, int T, int n, int act,
+                         cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && n > 0 && ld >= n, "unary_cast: bad sizes");
+  if (T == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(unary_cast_kernel<E>, dim3(T), dim3(128), 0, stream, in,
+      ld, (E*)out, n, act)));
+  return fb_check_launch("unary_cast");
+}

@@ -1,0 +1,233 @@
+// Grouped-query attention over the paged cache with a distance bias, a sliding
+// window that keeps the first tokens, and a softmax with a sink; with a norm
+// of the whole query and key projections in front of it.
+//
+//   q' = q / sqrt(mean(q^2) + eps) * wq     over ALL query rows of a token at once
+//   k' = k / sqrt(mean(k^2) + eps) * wk     (before the split into heads)
+//   s_ij = (q'_i . k'_j) * scale - slope_h * (i - j),  slope_h = 2^(-steep (h+1) / H)
+//   j visible to i  iff  j <= i and (i - j < window or j < keep_first)
+//   p_ij = exp(s_ij) / (sink + sum_j exp(s_ij)),  sink = 1 or 0: a key of score 0
+//          that has no value
+//   o_i = sum_j p_ij v_j
+//
+// Every constant is a parameter: window 0 = all earlier keys, steep 0 = no bias,
+// sink 0 = the plain softmax. Keys have `dim` elements and values `vdim`; the
+// two caches have strides of their own. Positions are the tokens' own, so a
+// kept token keeps its true distance.
+//
+// This file holds the CUDA-core forms (32-bit arithmetic, any sizes): one warp
+// per (token, query head) walking the kept prefix and then the window.
+#include "common.cuh"
+
+namespace {
+constexpr int WARPS = 4;
+constexpr int MAX_D = 256;
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = __ldcg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldcg(reinterpret_cast<const float4*>(p + 4));
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+// ------------------------------------------------ whole-projection norm + cache
+template <typename T>
+__global__ void qk_norm_cache_kernel(const float* qkv, long long ld, T* __restrict__ q_out,
+                                     const float* __restrict__ wq, const float* __restrict__ wk,
+                                     float eps, const int* __restrict__ positions,
+                                     const int* __restrict__ seq_of_token,
+                                     const int* __restrict__ page_table, int max_pages,
+                                     T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                     long long k_page, long long k_head, long long v_page,
+                                     long long v_head, int H, int G, int dim, int vdim,
+                                     int write_cache) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int seq = seq_of_token[t];
+  const int nq = H * dim, nk = G * dim, nv = G * vdim;
+  const float* row = qkv + (size_t)t * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+    const float v = __ldcg(row + i);
+    sq += v * v;
+  }
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const float v = __ldcg(row + nq + i);
+    sk += v * v;
+  }
+  sq = fb_block_sum(sq, scratch);
+  sk = fb_block_sum(sk, scratch);
+  const float rq = 1.0f / sqrtf(sq / (float)nq + eps);
+  const float rk = 1.0f / sqrtf(sk / (float)nk + eps);
+  T* qo = q_out + (size_t)t * nq;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x)
+    qo[i] = fb_from_float<T>(__ldcg(row + i) * rq * wq[i]);
+  if (!write_cache || seq < 0) return;
+  const int pos = positions[t];
+  const long long page = page_table[(size_t)seq * max_pages + pos / FB_PAGE];
+  const int r = pos % FB_PAGE;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int g = i / dim, d = i - g * dim;
+    k_cache[page * k_page + g * k_head + (long long)r * dim + d] =
+        fb_from_float<T>(__ldcg(row + nq + i) * rk * wk[i]);
+  }
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const int g = i / vdim, d = i - g * vdim;
+    v_cache[page * v_page + g * v_head + (long long)r * vdim + d] =
+        fb_from_float<T>(__ldcg(row + nq + nk + i));
+  }
+}
+
+// ---------------------------------------------------------------- attention
+struct SinkMask {
+  int window, keep_first, sink;
+  float scale, steep;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long long out_stride,
+                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                      const int* __restrict__ page_table, int max_pages, const T* k_cache,
+                      const T* v_cache, long long k_page, long long k_head, long long v_page,
+                      long long v_head, SinkMask mask, int H, int G, int D, int VD) {
+  fb_pdl_wait();
+  __shared__ float qs[WARPS][MAX_D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int a = blockIdx.y * WARPS + warp;
+  if (a >= H) return;
+  const int seq = seq_of_token[t];
+  T* o = out + (size_t)t * out_stride + (size_t)a * VD;
+  if (seq < 0) {  // padding token: defined output, no cache access
+    for (int d = lane; d < VD; d += 32) o[d] = fb_from_float<T>(0.f);
+    return;
+  }
+  const int pos = positions[t];
+  const int g = a / (H / G);
+  const T* qrow = q + (size_t)t * q_stride + (size_t)a * D;
+  for (int d = lane; d < D; d += 32) qs[warp][d] = fb_load_coherent<T>(qrow + d);
+  __syncwarp();
+  const float slope = mask.steep > 0.f ? exp2f(-mask.steep * (float)(a + 1) / (float)H) : 0.f;
+  const int lo = (mask.window > 0 && pos - mask.window + 1 > 0) ? pos - mask.window + 1 : 0;
+  const int kept = min(mask.keep_first, lo);  // keys [0, kept) lie in front of the window
+  const int* pages = page_table + (size_t)seq * max_pages;
+  const T* kbase = k_cache + (long long)g * k_head;
+  const T* vbase = v_cache + (long long)g * v_head;
+
+  // the sink is a key of score 0 without a value: it starts the running maximum and sum
+  float m = mask.sink ? 0.f : -INFINITY, l = mask.sink ? 1.f : 0.f;
+  float acc[MAX_D / 32];
+#pragma unroll
+  for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
+
+  for (int range = 0; range < 2; ++range) {
+    const int begin = range == 0 ? 0 : lo;
+    const int end = range == 0 ? kept : pos + 1;  // exclusive
+    for (int j0 = begin; j0 < end; j0 += 32) {
+      const int j = j0 + lane;
+      float s = -INFINITY;
+      long long k_off = 0, v_off = 0;
+      if (j < end) {
+        const long long page = pages[j / FB_PAGE];
+        const int r = j % FB_PAGE;
+        k_off = page * k_page + (long long)r * D;
+        v_off = page * v_page + (long long)r * VD;
+        const T* krow = kbase + k_off;
+        float dot = 0.f;
+        for (int d = 0; d < D; d += 8) {
+          float kv[8];
+          load8<T>(krow + d, kv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot = fmaf(qs[warp][d + e], kv[e], dot);
+        }
+        s = dot * mask.scale - slope * (float)(pos - j);
+      }
+      const float m_new = fmaxf(m, fb_warp_max(s));
+      const float corr = expf(m - m_new);  // exp(-inf) = 0 on a first chunk without sink
+      const float p = (j < end) ? expf(s - m_new) : 0.f;
+      l = l * corr + fb_warp_sum(p);
+      m = m_new;
+#pragma unroll
+      for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= corr;
+      const int n = min(32, end - j0);
+      for (int jj = 0; jj < n; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, p, jj);
+        const long long off = __shfl_sync(0xffffffffu, v_off, jj);
+        const T* vrow = vbase + off;
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (d < VD) acc[i] = fmaf(pj, fb_load_coherent<T>(vrow + d), acc[i]);
+        }
+      }
+    }
+  }
+  const float inv_l = 1.0f / l;
+#pragma unroll
+  for (int i = 0; i < MAX_D / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < VD) o[d] = fb_from_float<T>(acc[i] * inv_l);
+  }
+}
+}  // namespace
+
+FB_API int fb_qk_norm_cache_write(const float* qkv, long long ld, void* q_out, int dtype,
+                                  const float* wq, const float* wk, float eps,
+                                  const int* positions, const int* seq_of_token,
+                                  const int* page_table, int max_pages, void* k_cache,
+                                  void* v_cache, long long k_page, long long k_head,
+                                  long long v_page, long long v_head, int T, int H, int G, int dim,
+                                  int vdim, int write_cache, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && H > 0 && G > 0 && dim > 0 && vdim > 0, "qk_norm_cache_write: bad sizes");
+  FB_REQUIRE(ld >= (long long)H * dim + (long long)G * (dim + vdim),
+             "qk_norm_cache_write: rows of %lld hold no q, k and v", ld);
+  FB_REQUIRE(!write_cache || (k_cache && v_cache && page_table && max_pages > 0),
+             "qk_norm_cache_write: no cache to write");
+  if (T == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(qk_norm_cache_kernel<E>, dim3(T), dim3(256), 0, stream,
+      qkv, ld, (E*)q_out, wq, wk, eps, positions, seq_of_token, page_table, max_pages,
+      (E*)k_cache, (E*)v_cache, k_page, k_head, v_page, v_head, H, G, dim, vdim, write_cache)));
+  return fb_check_launch("qk_norm_cache_write");
+}
+
+FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long long out_stride,
+                             int dtype, const int* positions, const int* seq_of_token,
+                             const int* page_table, int max_pages, const void* k_cache,
+                             const void* v_cache, long long k_page, long long k_head,
+                             long long v_page, long long v_head, int window, int keep_first,
+                             int sink, float scale, float steep, int T, int H, int G, int D, int VD,
+                             cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && H > 0 && G > 0 && D > 0 && VD > 0, "attention_sink: bad sizes");
+  FB_REQUIRE(H % G == 0, "attention_sink: %d query heads are not a multiple of %d key-value heads",
+             H, G);
+  FB_REQUIRE(D % 8 == 0 && D <= MAX_D && VD <= MAX_D,
+             "attention_sink: key size %d must be a multiple of 8, and both sizes at most %d "
+             "(value size %d)", D, MAX_D, VD);
+  FB_REQUIRE(k_page % 8 == 0 && k_head % 8 == 0, "attention_sink: key rows are not 16-byte aligned");
+  FB_REQUIRE(window >= 0 && keep_first >= 0 && max_pages > 0, "attention_sink: bad mask");
+  if (T == 0) return 0;
+  SinkMask mask{window, keep_first, sink ? 1 : 0, scale, steep};
+  dim3 grid(T, (H + WARPS - 1) / WARPS);
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E>, dim3(grid), dim3(WARPS * 32), 0,
+      stream, (const E*)q, q_stride, (E*)out, out_stride, positions, seq_of_token, page_table,
+      max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head, v_page, v_head, mask, H, G,
+      D, VD)));
+  return fb_check_launch("attention_sink");
+}

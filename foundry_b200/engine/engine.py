@@ -76,8 +76,11 @@ class Engine:
                     max_tokens: int = 8192, max_slots: int = 256) -> "Engine":
         """config.json picks the architecture; model.safetensors gives the weights."""
         arch, config = load_model_config(model_dir)
+        files = WeightFiles.open(model_dir)
+        if arch.complete_from_files is not None:  # sizes that only the tensors' shapes give
+            config = arch.complete_from_files(config, files)
         engine = cls(arch.build_spec(config), config, dtype, device, max_tokens, max_slots)
-        engine.model.load(WeightFiles.open(model_dir))
+        engine.model.load(files)
         engine._make_cache()
         return engine
 

@@ -15,7 +15,7 @@ import torch
 from ..cache.store import CacheRequest, SequenceCache
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..parts import BLOCKS, NORMS
+from ..parts import BLOCKS, EMBEDDINGS, JUNCTIONS, NORMS
 from ..parts.base import first_weight_of
 from ..parts.linear import matmul_nt
 from ..weights.loader import ExpectedTensor, check_against, load_tensor
@@ -40,6 +40,11 @@ class Model:
         self.spec, self.dtype, self.device = spec, dtype, device
         self.blocks = _build_blocks(spec, dtype, device)
         self.final_norm = NORMS.build(spec.final_norm, dtype=dtype, device=device)
+        self.embedder = (EMBEDDINGS.build(spec.embedding, dtype=dtype, device=device)
+                         if spec.embedding is not None else None)
+        self.junctions = [JUNCTIONS.build(j, dtype=dtype, device=device) for j in spec.junctions]
+        if len(spec.junction_prefixes) != len(self.junctions):
+            raise ValueError("every junction needs a tensor-name prefix")
         self.embedding: Optional[torch.Tensor] = None
         self.output_head: Optional[torch.Tensor] = None
 
@@ -49,6 +54,8 @@ class Model:
         out = {spec.embedding_name: ExpectedTensor((spec.vocab_size, spec.hidden_size))}
         for block in self.blocks:
             out.update(block.expected_tensors())
+        for junction, prefix in zip(self.junctions, spec.junction_prefixes):
+            out.update(junction.expected_tensors(prefix))
         out.update(self.final_norm.expected_tensors(spec.final_norm_prefix))
         if spec.output_head_name is not None:
             out[spec.output_head_name] = ExpectedTensor((spec.vocab_size, spec.hidden_size))
@@ -81,6 +88,8 @@ class Model:
         self.embedding = fetch(spec.embedding_name).contiguous()
         for block in self.blocks:
             block.load(block.prefix, fetch)
+        for junction, prefix in zip(self.junctions, spec.junction_prefixes):
+            junction.load(prefix, fetch)
         self.final_norm.load(spec.final_norm_prefix, fetch)
         self.output_head = (self.embedding if spec.output_head_name is None
                             else fetch(spec.output_head_name).contiguous())
@@ -112,11 +121,14 @@ class Model:
         on the host (`replay_safe = True`, see parts/base.py): only then may a
         step of this model be captured once and replayed."""
         for block in self.blocks:
-            parts = [block] + [getattr(block, name, None) for name in
-                               ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")]
+            listed = getattr(block, "parts", None)  # a block may list its parts itself
+            parts = [block] + (list(listed()) if callable(listed) else
+                               [getattr(block, name, None) for name in
+                                ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")])
             if not all(p is not None and getattr(p, "replay_safe", False) for p in parts):
                 return False
-        return bool(getattr(self.final_norm, "replay_safe", False))
+        others = [self.final_norm] + self.junctions + ([self.embedder] if self.embedder else [])
+        return all(getattr(p, "replay_safe", False) for p in others)
 
     # --------------------------------------------------------------- cache
     def cache_requests(self) -> Dict[int, CacheRequest]:
@@ -138,10 +150,20 @@ class Model:
             shared.clear()  # what an earlier step on this context left
         resid = torch.empty((ctx.n_tokens, spec.hidden_size), dtype=torch.float32,
                             device=self.device)
-        ops.embed_gather(self.embedding, ctx.token_ids, resid)
+        # a junction may read the stream as the embedding left it
+        x0 = torch.empty_like(resid) if self.junctions else None
+        if self.embedder is None:
+            ops.embed_gather(self.embedding, ctx.token_ids, resid)
+            if x0 is not None:
+                x0.copy_(resid)
+        else:
+            self.embedder.forward(ctx, self.embedding, resid, x0)
         delta = None
         for i, entry in enumerate(spec.schedule):
             block = self.blocks[entry.layer]
+            if entry.junction is not None:
+                which, number = entry.junction
+                delta = self.junctions[which].forward(ctx, resid, delta, x0, number)
             follower = (self.blocks[spec.schedule[i + 1].layer] if i + 1 < len(spec.schedule)
                         else None)
             ctx.reads_after_part = (first_weight_of(follower) if follower is not None
@@ -159,6 +181,12 @@ class Model:
         rows = torch.empty((n, spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.gather_rows(resid, ctx.want_rows, rows)
         rows_delta = None
+        if isinstance(delta, ops.NormedDelta):
+            # a last output whose own norm is still to come: that norm works row by row,
+            # so it is applied to the wanted rows only, by the final norm's pass
+            values = torch.empty((n, spec.hidden_size), dtype=delta.values.dtype, device=self.device)
+            ops.gather_rows(delta.values, ctx.want_rows, values)
+            rows_delta, delta = ops.NormedDelta(values, delta.weight, delta.bias, delta.eps), None
         if isinstance(delta, ops.Planes):
             delta = delta.sum(self.dtype)
         if delta is not None:

@@ -84,6 +84,35 @@ _SIGNATURES = {
     "fb_row_scales": [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
+    "fb_ln_add_ln": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_int, c_int, c_int, c_float, c_void_p],
+    "fb_embed_sinusoid": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_void_p],
+    "fb_concat_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "fb_add_row_vector": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "fb_qk_norm_cache_write": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_ll,
+                               c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "fb_attention_sink": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
+                          c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_int,
+                          c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "fb_token_shift_mix": [c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "fb_state_tail_update": [c_void_p, c_int, c_ll, c_void_p, c_ll, c_ll, c_int, c_int, c_void_p,
+                             c_void_p, c_int, c_void_p],
+    "fb_conv_silu_unit": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_int,
+                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                          c_int, c_void_p],
+    "fb_decay_gate": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "fb_state_scan": [c_int, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll,
+                      c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
+                      c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "fb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_float, c_void_p,
+                          c_int, c_int, c_int, c_int, c_void_p],
+    "fb_unary_cast": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "fb_moe_route": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "fb_moe_experts_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
 }
 
 _FUNCS = {}
@@ -1451,4 +1480,270 @@ def select_tokens(logits: torch.Tensor, out: torch.Tensor, temperature: Optional
           _dev(out, "out", torch.int32), chunks,
           0 if part_val is None else part_val.data_ptr(),
           0 if part_idx is None else part_idx.data_ptr(), _stream())
+    return out
+
+
+# --------------------------------------------------- layer norm, sinusoidal embedding
+class NormedDelta:
+    """The output of a part that still has to pass a layer norm of its own
+    before it joins the residual: resid += LN(values; weight, bias). The norm
+    that follows in the stream makes this sum in its own pass over the row
+    (`ln_add_ln`); `settle` makes it alone."""
+
+    def __init__(self, values: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float):
+        self.values, self.weight, self.bias, self.eps = values, weight, bias, float(eps)
+
+    def settle(self, resid: torch.Tensor) -> None:
+        ln_add_ln(resid, self, None, None, self.eps, None)
+        return None
+
+
+def ln_add_ln(resid: torch.Tensor, pending: Optional[NormedDelta], weight: Optional[torch.Tensor],
+              bias: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor]):
+    """resid += LN(pending.values) where `pending` is given, then
+    out = LN(resid; weight, bias) where `out` is given; float32 statistics."""
+    T, W = resid.shape
+    y = w1 = b1 = 0
+    y_code = F32
+    if pending is not None:
+        if tuple(pending.values.shape) != (T, W) or pending.eps != float(eps):
+            raise KernelError(f"ln_add_ln: pending rows {tuple(pending.values.shape)} eps "
+                              f"{pending.eps} for resid {(T, W)} eps {eps}")
+        y, y_code = _dev(pending.values, "values"), code_of(pending.values.dtype)
+        if pending.weight is not None:  # else a plain sum
+            w1 = _dev(pending.weight, "weight", torch.float32)
+            b1 = _dev(pending.bias, "bias", torch.float32)
+    o = w2 = b2 = 0
+    o_code = F32
+    if out is not None:
+        if tuple(out.shape) != (T, W) or tuple(weight.shape) != (W,) or tuple(bias.shape) != (W,):
+            raise KernelError(f"ln_add_ln: out {tuple(out.shape)}, weight {tuple(weight.shape)}")
+        o, o_code = _dev(out, "out"), code_of(out.dtype)
+        w2, b2 = _dev(weight, "weight", torch.float32), _dev(bias, "bias", torch.float32)
+    _call("fb_ln_add_ln", y, y_code, w1, b1, _dev(resid, "resid", torch.float32), w2, b2, o, o_code,
+          T, W, float(eps), _stream())
+    return out
+
+
+def embed_sinusoid(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+                   freq: torch.Tensor, scale: float, out: torch.Tensor,
+                   copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale + (sin, cos pairs of positions[t] * freq),
+    float32; `copy` receives the same rows."""
+    V, W = table.shape
+    T = ids.numel()
+    if out.shape != (T, W) or freq.numel() * 2 != W or (copy is not None and copy.shape != out.shape):
+        raise KernelError(f"embed_sinusoid: out {tuple(out.shape)}, table {tuple(table.shape)}")
+    _call("fb_embed_sinusoid", _dev(table, "table"), code_of(table.dtype),
+          _dev(ids, "ids", torch.int32), _dev(positions, "positions", torch.int32),
+          _dev(freq, "freq", torch.float64), float(scale), _dev(out, "out", torch.float32),
+          0 if copy is None else _dev(copy, "copy", torch.float32), T, W, V, _stream())
+    return out
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = [a[t]; b[t]] rounded to out's dtype (a, b float32 [T, W])."""
+    T, W = a.shape
+    if b.shape != a.shape or out.shape != (T, 2 * W):
+        raise KernelError("concat_cast: shapes differ")
+    _call("fb_concat_cast", _dev(a, "a", torch.float32), _dev(b, "b", torch.float32),
+          _dev(out, "out"), code_of(out.dtype), T, W, _stream())
+    return out
+
+
+def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    T, W = x.shape
+    if v.shape != (W,):
+        raise KernelError("add_row_vector: the vector does not fit the rows")
+    _call("fb_add_row_vector", _dev(x, "x", torch.float32), _dev(v, "v", torch.float32), T, W,
+          _stream())
+    return x
+
+
+# ------------------------------------------------ attention with bias, window and sink
+def qk_norm_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor,
+                        eps: float, positions, seq_of_token, page_table, k_cache, v_cache,
+                        H: int, G: int, dim: int, vdim: int, write_cache: bool = True):
+    """RMS norm over a token's whole query projection and whole key projection
+    (float32 `qkv` rows [q | k | v]); queries to `q_out`, keys and values into
+    the token's cache row. Caches are [pages, G, PAGE, dim] and [.., vdim]."""
+    T = qkv.shape[0]
+    kp = vp = 0
+    ks = vs = (0, 0)
+    if write_cache:
+        _check_kv_pair(k_cache, v_cache, G, dim, vdim, q_out.dtype)
+        kp, vp = k_cache.data_ptr(), v_cache.data_ptr()
+        ks, vs = (k_cache.stride(0), k_cache.stride(1)), (v_cache.stride(0), v_cache.stride(1))
+    _call("fb_qk_norm_cache_write", _dev(qkv, "qkv", torch.float32, contiguous=False),
+          _rows(qkv, "qkv"), _dev(q_out, "q_out"), code_of(q_out.dtype),
+          _dev(wq, "wq", torch.float32), _dev(wk, "wk", torch.float32), float(eps),
+          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1], kp, vp, *ks, *vs,
+          T, H, G, dim, vdim, 1 if write_cache else 0, _stream())
+    return q_out
+
+
+def _check_kv_pair(k_cache, v_cache, G, dim, vdim, dtype) -> None:
+    for name, c, d in (("k_cache", k_cache, dim), ("v_cache", v_cache, vdim)):
+        if c is None or not c.is_cuda or c.dtype != dtype:
+            raise KernelError(f"{name} must be a CUDA tensor of dtype {dtype}")
+        if c.dim() != 4 or tuple(c.shape[1:]) != (G, PAGE, d) or c.stride(3) != 1 or c.stride(2) != d:
+            raise KernelError(f"{name} is {tuple(c.shape)} strides {c.stride()}, expected "
+                              f"[pages, {G}, {PAGE}, {d}] with contiguous rows")
+
+
+def attention_sink(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache, v_cache, H: int,
+                   G: int, dim: int, vdim: int, scale: float, window: int = 0, keep_first: int = 0,
+                   sink: bool = False, steep: float = 0.0) -> torch.Tensor:
+    """Causal attention of every token of the step over its sequence's cache,
+    with the mask, bias and sink of csrc/sink_attention.cu."""
+    T = q.shape[0]
+    _check_kv_pair(k_cache, v_cache, G, dim, vdim, q.dtype)
+    _call("fb_attention_sink", _dev(q, "q", contiguous=False), _rows(q, "q"),
+          _dev(out, "out", q.dtype, contiguous=False), _rows(out, "out"), code_of(q.dtype),
+          _dev(ctx.positions, "positions", torch.int32),
+          _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1],
+          k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
+          v_cache.stride(0), v_cache.stride(1), int(window or 0), int(keep_first or 0),
+          1 if sink else 0, float(scale), float(steep), T, H, G, dim, vdim, _stream())
+    return out
+
+
+# ---------------------------------------------------- mixers with a carried state
+class StateRows:
+    """One cache entry's state rows [slots, floats] seen as named float32
+    fields: `offset[name]` floats into a sequence's row."""
+
+    def __init__(self, rows: torch.Tensor, fields):
+        if rows.dtype != torch.float32 or rows.dim() != 2 or not rows.is_contiguous():
+            raise KernelError("state rows must be contiguous float32 [slots, floats]")
+        self.rows, self.stride = rows, rows.stride(0)
+        self.offset, at = {}, 0
+        for name, count in fields:
+            self.offset[name] = at
+            at += int(count)
+        if at > rows.shape[1]:
+            raise KernelError(f"state fields take {at} floats, a row holds {rows.shape[1]}")
+
+
+def token_shift_mix(ctx, h: torch.Tensor, state: StateRows, field: str, mu: torch.Tensor,
+                    out: torch.Tensor) -> torch.Tensor:
+    """out[m, t] = h[t] + (h[t-1] - h[t]) * mu[m]; a sequence's row before the
+    step is state field `field`."""
+    T, W = h.shape
+    n = mu.shape[0]
+    if out.shape != (n, T, W) or mu.shape != (n, W) or out.dtype != h.dtype:
+        raise KernelError("token_shift_mix: shapes differ")
+    _call("fb_token_shift_mix", _dev(h, "h"), code_of(h.dtype), state.rows.data_ptr(), state.stride,
+          state.offset[field], _dev(mu, "mu", torch.float32), _dev(out, "out"),
+          _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
+          _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.slots, "slots", torch.int32),
+          T, W, n, _stream())
+    return out
+
+
+def state_tail_update(ctx, x: torch.Tensor, state: StateRows, field: str, n_tail: int,
+                      channels: int) -> None:
+    """state[field] ([n_tail, channels]) <- the last n_tail rows of what it held
+    followed by the step's rows of `x` (first `channels` columns), per sequence."""
+    _call("fb_state_tail_update", _dev(x, "x", contiguous=False), code_of(x.dtype), _rows(x, "x"),
+          state.rows.data_ptr(), state.stride, state.offset[field], n_tail, channels,
+          _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.slots, "slots", torch.int32),
+          ctx.n_seqs, _stream())
+
+
+def conv_silu_unit(ctx, x: torch.Tensor, weight: torch.Tensor, state: StateRows, field: str,
+                   out: torch.Tensor, channels: int, n_unit: int, dim: int, n_scaled: int,
+                   extra: float, unit_eps: float) -> torch.Tensor:
+    """Causal convolution over time per channel, SiLU, then unit-length heads
+    (csrc/sequence_mix.cu). `x` float32 rows (first `channels` columns are used)."""
+    T = x.shape[0]
+    taps = weight.shape[1]
+    if weight.shape[0] != channels or out.shape != (T, channels):
+        raise KernelError("conv_silu_unit: shapes differ")
+    _call("fb_conv_silu_unit", _dev(x, "x", torch.float32, contiguous=False), _rows(x, "x"),
+          _dev(weight, "weight", torch.float32), taps, state.rows.data_ptr(), state.stride,
+          state.offset[field], _dev(out, "out", torch.float32), channels,
+          _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
+          _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.slots, "slots", torch.int32),
+          n_unit, dim, n_scaled, float(extra), float(unit_eps), T, _stream())
+    return out
+
+
+def decay_gate(x: torch.Tensor, per_head: int, bias: torch.Tensor, A: Optional[torch.Tensor]):
+    """In place on float32 [T, n]: with `A` ([heads]) exp(-exp(A) softplus(x + bias)),
+    without it exp(-exp(x + bias))."""
+    T, n = x.shape
+    if bias.numel() != n:
+        raise KernelError("decay_gate: the bias does not fit the rows")
+    _call("fb_decay_gate", _dev(x, "x", torch.float32), T, n, per_head,
+          0 if A is None else _dev(A, "A", torch.float32), _dev(bias, "bias", torch.float32),
+          1 if A is None else 0, _stream())
+    return x
+
+
+SCAN_DELTA, SCAN_WKV = 0, 1
+
+
+def state_scan(ctx, mode: int, q, k, v, g, state: StateRows, field: str, out: torch.Tensor,
+               H: int, rep: int, dim: int, vdim: int, beta=None, bonus=None) -> torch.Tensor:
+    """The recurrence of csrc/sequence_mix.cu over every sequence of the step.
+    q, k: float32 views [T, >= (H / rep) * dim]; v [T, >= H * vdim]; g [T, H * dim];
+    beta (delta) a float32 view [T, >= H]; bonus (wkv) [H, dim]; out float32 [T, H * vdim]."""
+    T = out.shape[0]
+    if out.shape != (T, H * vdim) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("state_scan: out must be contiguous float32 [T, heads * vdim]")
+    f32 = torch.float32
+    _call("fb_state_scan", mode, _dev(q, "q", f32, contiguous=False), _rows(q, "q"),
+          _dev(k, "k", f32, contiguous=False), _rows(k, "k"),
+          _dev(v, "v", f32, contiguous=False), _rows(v, "v"),
+          _dev(g, "g", f32, contiguous=False), _rows(g, "g"),
+          0 if beta is None else _dev(beta, "beta", f32, contiguous=False),
+          0 if beta is None else _rows(beta, "beta"),
+          0 if bonus is None else _dev(bonus, "bonus", f32), state.rows.data_ptr(), state.stride,
+          state.offset[field], out.data_ptr(), _dev(ctx.cu_tokens, "cu_tokens", torch.int32),
+          _dev(ctx.slots, "slots", torch.int32), ctx.n_seqs, H, rep, dim, vdim, _stream())
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, per_head_weight: bool, gate: torch.Tensor,
+                   act: str, eps: float, out: torch.Tensor, H: int, vdim: int) -> torch.Tensor:
+    """out = o / rms(o per head) * weight * act(gate); act "sigmoid" or "silu"."""
+    T = o.shape[0]
+    _call("fb_head_norm_gate", _dev(o, "o", torch.float32), _dev(weight, "weight", torch.float32),
+          vdim if per_head_weight else 0, _dev(gate, "gate", torch.float32, contiguous=False),
+          _rows(gate, "gate"), {"sigmoid": 0, "silu": 1}[act], float(eps), _dev(out, "out"),
+          code_of(out.dtype), T, H, vdim, _stream())
+    return out
+
+
+def unary_cast(x: torch.Tensor, out: torch.Tensor, act: str = "identity") -> torch.Tensor:
+    """out = act(x) rounded to out's dtype; x float32 rows (possibly strided)."""
+    T, n = out.shape
+    _call("fb_unary_cast", _dev(x, "x", torch.float32, contiguous=False), _rows(x, "x"),
+          _dev(out, "out"), code_of(out.dtype), T, n, {"identity": 0, "tanh": 1}[act], _stream())
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+def moe_route(z: torch.Tensor, bias: torch.Tensor, top: int, chosen: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    T, E = z.shape
+    _call("fb_moe_route", _dev(z, "z", torch.float32, contiguous=False), _rows(z, "z"),
+          _dev(bias, "bias", torch.float32), E, top, _dev(chosen, "chosen", torch.int32),
+          _dev(weights, "weights", torch.float32), T, _stream())
+
+
+def moe_experts_rows(h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
+                     chosen: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, limit: float,
+                     alpha: float) -> torch.Tensor:
+    T, W = h.shape
+    E, two_ff, _ = gate_up.shape
+    if gate_up.dtype != h.dtype or down.dtype != h.dtype or down.shape != (E, W, two_ff // 2):
+        raise KernelError("moe_experts_rows: the experts' matrices do not fit the input")
+    _call("fb_moe_experts_rows", _dev(h, "h"), code_of(h.dtype), _dev(gate_up, "gate_up"),
+          _dev(down, "down"), _dev(chosen, "chosen", torch.int32),
+          _dev(weights, "weights", torch.float32), _dev(out, "out", torch.float32), T, W,
+          two_ff // 2, chosen.shape[1], E, float(limit), float(alpha), _stream())
     return out

@@ -2,16 +2,20 @@
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Part, Registry,
                    register_block, register_feed_forward, register_mixer, register_norm,
                    register_position_encoding)
-from . import attention, block, linear, mlp, norm, rope  # noqa: F401  (registration)
+from . import (attention, block, embedding, junction, linear, mlp, moe, norm,  # noqa: F401
+               recurrent, rope, sink_attention)  # (registration)
+from .embedding import EMBEDDINGS, register_embedding
+from .junction import JUNCTIONS, register_junction
 from .attention import GQAAttention
 from .block import PreNormResidualBlock
 from .linear import Linear, matmul_nt
 from .mlp import SwiGLU
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 from .rope import Rope, RopeLlama3, llama3_inv_freq, plain_inv_freq
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Part", "Registry",
            "register_block", "register_feed_forward", "register_mixer", "register_norm",
-           "register_position_encoding", "GQAAttention", "PreNormResidualBlock", "Linear",
+           "register_position_encoding", "EMBEDDINGS", "JUNCTIONS", "register_embedding",
+           "register_junction", "LayerNorm", "GQAAttention", "PreNormResidualBlock", "Linear",
            "matmul_nt", "SwiGLU", "RMSNorm", "Rope", "RopeLlama3", "llama3_inv_freq",
            "plain_inv_freq"]

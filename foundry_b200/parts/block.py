@@ -86,3 +86,81 @@ def _sink_for(norm, consumer, resid: torch.Tensor):
     if not callable(offer) or not getattr(consumer, "accepts_row_scaled", False):
         return None
     return offer(resid)
+
+
+@register_block("sandwich_norm_residual")
+class SandwichNormBlock(Part):
+    """A norm in front of AND behind each part:
+
+        x <- x + post1(mixer(pre1(x)));  x <- x + post2(feed_forward(pre2(x)))
+
+    the second line only where the layer has a feed-forward. A part's output
+    leaves as an `ops.NormedDelta` (its post-norm still to be applied) and the
+    norm that runs next makes `x += post(y)` and its own normalisation in one
+    pass over the row, so the block, like `pre_norm_residual`, returns its last
+    output un-added. The residual stream and all statistics are 32-bit."""
+    replay_safe = True
+
+    def __init__(self, layer: LayerSpec, *, dtype: torch.dtype, device: torch.device):
+        ctx = dict(dtype=dtype, device=device)
+        if layer.mixer_post_norm is None:
+            raise ValueError("sandwich_norm_residual needs a norm behind the mixer")
+        self.prefix = layer.prefix
+        self.names = dict(layer.names)
+        self.mixer = MIXERS.build(layer.mixer, **ctx)
+        self.mixer_norm = NORMS.build(layer.mixer_norm, **ctx)
+        self.mixer_post_norm = NORMS.build(layer.mixer_post_norm, **ctx)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if layer.feed_forward is not None:
+            if layer.feed_forward_norm is None or layer.feed_forward_post_norm is None:
+                raise ValueError("sandwich_norm_residual needs both norms of the feed-forward")
+            self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, **ctx)
+            self.feed_forward_norm = NORMS.build(layer.feed_forward_norm, **ctx)
+            self.feed_forward_post_norm = NORMS.build(layer.feed_forward_post_norm, **ctx)
+
+    def _named(self):
+        p, n = self.prefix, self.names
+        named = [(self.mixer_norm, f"{p}.{n['mixer_norm']}"), (self.mixer, f"{p}.{n['mixer']}"),
+                 (self.mixer_post_norm, f"{p}.{n['mixer_post_norm']}")]
+        if self.feed_forward is not None:
+            named += [(self.feed_forward_norm, f"{p}.{n['feed_forward_norm']}"),
+                      (self.feed_forward, f"{p}.{n['feed_forward']}"),
+                      (self.feed_forward_post_norm, f"{p}.{n['feed_forward_post_norm']}")]
+        return named
+
+    def parts(self):
+        """Every part of the block (for whoever asks them all something)."""
+        return [part for part, _ in self._named()]
+
+    def expected_tensors(self, prefix: str = "") -> Dict[str, ExpectedTensor]:
+        out: Dict[str, ExpectedTensor] = {}
+        for part, name in self._named():
+            out.update(part.expected_tensors(name))
+        return out
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        for part, name in self._named():
+            part.load(name, fetch)
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def first_weight(self):
+        return first_weight_of(self.mixer)
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache):
+        ctx.reads_after_part = None
+        ctx.residual_sink = None  # these norms are not the kind a projection can take over
+        normed = self.mixer_norm.add_norm(resid, delta)
+        mixed = _as_rows(self.mixer.forward(ctx, normed, cache))
+        pending = self.mixer_post_norm.pending(mixed)
+        if self.feed_forward is None:
+            return pending
+        normed = self.feed_forward_norm.add_norm(resid, pending)
+        return self.feed_forward_post_norm.pending(_as_rows(self.feed_forward.forward(ctx, normed)))
+
+
+def _as_rows(y):
+    """A part's output as one tensor (split-K planes are summed in 32-bit)."""
+    from ..kernels import ops
+    return y.sum(torch.float32) if isinstance(y, ops.Planes) else y

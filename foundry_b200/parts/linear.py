@@ -43,19 +43,20 @@ class Linear(Part):
     """One or more named [out_i, in] matrices applied as a single product."""
 
     def __init__(self, in_features: int, outs: Sequence[Tuple[str, int]], *, dtype: torch.dtype,
-                 device: torch.device):
+                 device: torch.device, suffix: str = ".weight"):
         self.in_features = in_features
+        self.suffix = suffix  # what follows a projection's name in the weight files
         self.outs = list(outs)  # (name suffix such as "q_proj", rows)
         self.out_features = sum(n for _, n in self.outs)
         self.dtype, self.device = dtype, device
         self.weight: Optional[torch.Tensor] = None
 
     def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
-        return {f"{prefix}.{name}.weight": ExpectedTensor((rows, self.in_features))
+        return {f"{prefix}.{name}{self.suffix}": ExpectedTensor((rows, self.in_features))
                 for name, rows in self.outs}
 
     def load(self, prefix: str, fetch: Fetch) -> None:
-        parts = [fetch(f"{prefix}.{name}.weight") for name, _ in self.outs]
+        parts = [fetch(f"{prefix}.{name}{self.suffix}") for name, _ in self.outs]
         kinds = {p.dtype for p in parts}
         if len(kinds) != 1:
             raise ops.KernelError(f"{prefix}: fused projections are stored in different dtypes")

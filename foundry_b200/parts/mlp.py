@@ -20,21 +20,24 @@ class SwiGLU(Part):
     accepts_row_scaled = True  # the gate/up product applies a deferred norm's row scale
 
     def __init__(self, hidden_size: int, intermediate_size: int, *, dtype: torch.dtype,
-                 device: torch.device):
+                 device: torch.device, names=("gate_proj", "up_proj", "down_proj"),
+                 suffix: str = ".weight"):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.dtype, self.device = dtype, device
+        self.names, self.suffix = tuple(names), suffix  # the three projections in the files
         self.gate_up: torch.Tensor = None  # [2I, H]: row 2i is gate i, row 2i+1 is up i
-        self.down = Linear(intermediate_size, [("down_proj", hidden_size)], dtype=dtype,
-                           device=device)
+        self.down = Linear(intermediate_size, [(self.names[2], hidden_size)], dtype=dtype,
+                           device=device, suffix=suffix)
 
     def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
         shape = (self.intermediate_size, self.hidden_size)
-        return {f"{prefix}.gate_proj.weight": ExpectedTensor(shape),
-                f"{prefix}.up_proj.weight": ExpectedTensor(shape),
+        return {f"{prefix}.{self.names[0]}{self.suffix}": ExpectedTensor(shape),
+                f"{prefix}.{self.names[1]}{self.suffix}": ExpectedTensor(shape),
                 **self.down.expected_tensors(prefix)}
 
     def load(self, prefix: str, fetch: Fetch) -> None:
-        gate, up = fetch(f"{prefix}.gate_proj.weight"), fetch(f"{prefix}.up_proj.weight")
+        gate = fetch(f"{prefix}.{self.names[0]}{self.suffix}")
+        up = fetch(f"{prefix}.{self.names[1]}{self.suffix}")
         if gate.dtype != up.dtype:
             raise ops.KernelError(f"{prefix}: gate and up projections are stored in different dtypes")
         # rows interleaved so that a product tile holds matching gate / up pairs

@@ -48,3 +48,46 @@ class RMSNorm(Part):
         if out is None:
             out = torch.empty(resid.shape, dtype=self.dtype, device=resid.device)
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
+
+
+@register_norm("layer_norm")
+class LayerNorm(Part):
+    """(x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b with 32-bit statistics
+    (csrc/layernorm.cu). The tensors are `<prefix><weight_suffix>` and
+    `<prefix><bias_suffix>`. Beside normalising a part's input (`add_norm`) it
+    may stand behind a part: `pending(y)` says that LN(y) is still to join the
+    residual, and the next `add_norm` (or `NormedDelta.settle`) makes that sum in
+    the same pass."""
+    replay_safe = True
+
+    def __init__(self, size: int, eps: float, weight_suffix: str = ".weight",
+                 bias_suffix: str = ".bias", *, dtype: torch.dtype, device: torch.device):
+        self.size, self.eps = size, float(eps)
+        self.weight_suffix, self.bias_suffix = weight_suffix, bias_suffix
+        self.dtype, self.device = dtype, device
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
+        return {f"{prefix}{self.weight_suffix}": ExpectedTensor((self.size,)),
+                f"{prefix}{self.bias_suffix}": ExpectedTensor((self.size,))}
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        self.weight = fetch(f"{prefix}{self.weight_suffix}").to(torch.float32).contiguous()
+        self.bias = fetch(f"{prefix}{self.bias_suffix}").to(torch.float32).contiguous()
+
+    def pending(self, values: torch.Tensor) -> ops.NormedDelta:
+        return ops.NormedDelta(values, self.weight, self.bias, self.eps)
+
+    def add_norm(self, resid: torch.Tensor, delta, out: Optional[torch.Tensor] = None):
+        """resid += delta (None, a tensor, split-K planes, or an `ops.NormedDelta`
+        whose norm is applied on the way); returns LN(resid) in the activation dtype."""
+        if isinstance(delta, ops.Planes):
+            delta = delta.sum(torch.float32)
+        if delta is not None and not isinstance(delta, ops.NormedDelta):
+            delta = ops.NormedDelta(delta, None, None, self.eps)  # a plain sum
+        if delta is not None and delta.eps != self.eps:  # one pass takes one eps
+            delta = delta.settle(resid)
+        if out is None:
+            out = torch.empty(resid.shape, dtype=self.dtype, device=resid.device)
+        return ops.ln_add_ln(resid, delta, self.weight, self.bias, self.eps, out)
