@@ -106,6 +106,10 @@ class RupotarConfig:
     loop: Optional[Tuple[int, int, int]] = None  # (start, stop, times)
     extra: Mapping[str, Any] = field(default_factory=dict, compare=False)
 
+    @property
+    def vocab_size(self) -> int:  # the name other parts of the library ask for
+        return self.vocab
+
     @classmethod
     def parse(cls, source) -> "RupotarConfig":
         doc = decode_json(source)
