@@ -132,10 +132,18 @@ struct AttnParams {
   const void* next;      // constant data to bring into L2 for the kernel after this one
   long long next_bytes;  // 0 = none
   int trigger_next;      // 1: let the next kernel's blocks be placed once a CTA's pages are in
+  // prompts, masked form only: a key j is seen from position i iff j <= i and
+  // (window == 0 or i - j < window or j < keep_first); scores lose
+  // 2^(-steep (head + 1) / A) per token of distance (steep 0: no bias); with `sink`
+  // the softmax has one more term of score 0 that carries no value
+  int window, keep_first, sink;
+  float steep;
 };
 
 // --------------------------------------------------------------------- prefill
-template <int D>
+// EXT: the masked form (window with kept first tokens, distance bias, sink); pages
+// that no query of the block can see are neither loaded nor worked.
+template <int D, bool EXT = false>
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_kernel(const AttnParams p) {
   fb_pdl_wait();
@@ -177,10 +185,19 @@ attn_prefill_kernel(const AttnParams p) {
   const __nv_bfloat16* kbase = p.k_cache + (long long)kvh * p.head_stride;
   const __nv_bfloat16* vbase = p.v_cache + (long long)kvh * p.head_stride;
 
+  // the pages the block walks: those of the kept first tokens, then from the page of
+  // the first query's window start on
+  const int kept_pages = (EXT && p.window > 0 && p.keep_first > 0) ? (p.keep_first + FB_PAGE - 1) / FB_PAGE : 0;
+  const int first_win_page = (EXT && p.window > 0) ? max(0, pos0 - p.window + 1) / FB_PAGE : 0;
+  const int first_page = kept_pages > 0 ? 0 : first_win_page;
+  auto next_page = [&](int pg) { return (pg + 1 < kept_pages) ? pg + 1 : max(pg + 1, first_win_page); };
+  const float slope_l2 = (EXT && p.steep > 0.f)
+      ? exp2f(-p.steep * (float)(head + 1) / (float)p.A) * 1.4426950408889634f : 0.f;
+
   load_tile<D>(sQ, p.q + (long long)(tok0 + row0) * p.q_stride + (long long)head * D, p.q_stride,
                64, rows_valid);
   {
-    const long long off = (long long)pages[0] * p.page_stride;
+    const long long off = (long long)pages[first_page] * p.page_stride;
     load_tile<D>(sK, kbase + off, D, 64, 64);
     load_tile<D>(sV, vbase + off, D, 64, 64);
   }
@@ -191,26 +208,32 @@ attn_prefill_kernel(const AttnParams p) {
 #pragma unroll
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  if (EXT && p.sink) { m[0] = m[1] = 0.f; l[0] = l[1] = 1.f; }  // the term of score 0
   const int qpos_lo = pos0 + warp * 16 + g;  // position of row g; row g + 8 is 8 further
 
-  for (int pg = 0; pg < n_pages; ++pg) {
-    const int st = pg & 1;
-    if (pg + 1 < n_pages) {
-      const long long off = (long long)pages[pg + 1] * p.page_stride;
+  int it = 0;
+  for (int pg = first_page; pg < n_pages; pg = next_page(pg), ++it) {
+    const int st = it & 1;
+    const int nxt = next_page(pg);
+    if (nxt < n_pages) {
+      const long long off = (long long)pages[nxt] * p.page_stride;
       load_tile<D>(sK + (st ^ 1) * 64 * D, kbase + off, D, 64, 64);
       load_tile<D>(sV + (st ^ 1) * 64 * D, vbase + off, D, 64, 64);
     }
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    if (pg == 0) {
+    if (it == 0) {
 #pragma unroll
       for (int k = 0; k < KT; ++k)
         ldsm_x4(qf[k], smem_u32(sQ + Swz<D>::off(warp * 16 + (lane & 15), k * 16 + (lane >> 4) * 8)));
     }
     const int key0 = pg * FB_PAGE;
-    // a warp whose every query lies before this page has nothing to add
-    if (key0 <= pos0 + warp * 16 + 15) {
+    // a warp whose every query lies before this page has nothing to add; nor has one
+    // whose every window begins behind it, unless the page holds kept tokens
+    if (key0 <= pos0 + warp * 16 + 15 &&
+        (!EXT || p.window == 0 || key0 < p.keep_first ||
+         key0 + FB_PAGE - 1 >= pos0 + warp * 16 - p.window + 1)) {
       const __nv_bfloat16* tK = sK + st * 64 * D;
       const __nv_bfloat16* tV = sV + st * 64 * D;
       float s[8][4];
@@ -228,7 +251,7 @@ attn_prefill_kernel(const AttnParams p) {
         }
       }
       // scale, mask, online softmax (in the log2 domain)
-      const bool need_mask = key0 + FB_PAGE - 1 > pos0 + warp * 16;
+      const bool need_mask = EXT || key0 + FB_PAGE - 1 > pos0 + warp * 16;
       float mx[2] = {m[0], m[1]};
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
@@ -238,6 +261,10 @@ attn_prefill_kernel(const AttnParams p) {
           if (need_mask) {
             const int key = key0 + n * 8 + 2 * t + (e & 1);
             const int qp = qpos_lo + (e >> 1) * 8;
+            if (EXT) {
+              v -= slope_l2 * (float)(qp - key);
+              if (p.window > 0 && qp - key >= p.window && key >= p.keep_first) v = -INFINITY;
+            }
             if (key > qp) v = -INFINITY;
           }
           s[n][e] = v;
@@ -251,7 +278,11 @@ attn_prefill_kernel(const AttnParams p) {
       }
       float corr[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < 2; ++r) corr[r] = exp2f(m[r] - mx[r]);  // 0 on the first page
+      for (int r = 0; r < 2; ++r) {
+        corr[r] = exp2f(m[r] - mx[r]);  // 0 on the first page
+        // (masked form without a sink: a row may have seen no key yet; nothing to rescale)
+        if (EXT && mx[r] == -INFINITY) { corr[r] = 1.f; mx[r] = 0.f; }
+      }
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
 #pragma unroll
@@ -266,7 +297,7 @@ attn_prefill_kernel(const AttnParams p) {
         sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
         sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
         l[r] = l[r] * corr[r] + sum[r];
-        m[r] = mx[r];
+        m[r] = (EXT && sum[r] == 0.f && l[r] == 0.f) ? -INFINITY : mx[r];  // still nothing seen
       }
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
@@ -784,16 +815,16 @@ attn_decode_kernel(const AttnParams p) {
   else if (p.splits > 1) merge_if_last<D>(p, seq, kvh, token, G);
 }
 
-template <int D>
+template <int D, bool EXT = false>
 int launch_prefill(const AttnParams& p, int q_blocks, cudaStream_t stream) {
   const int bytes = (64 + 4 * 64) * D * 2;
   static bool configured[64] = {};
   if (fb_first_use_on_device(configured)) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D, EXT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return fb_fail(2, "attention_prefill: %s", cudaGetErrorString(e));
   }
-  fb_launch(attn_prefill_kernel<D>, dim3(dim3(q_blocks, p.A)), dim3(THREADS), bytes, stream, p);
+  fb_launch(attn_prefill_kernel<D, EXT>, dim3(dim3(q_blocks, p.A)), dim3(THREADS), bytes, stream, p);
   return fb_check_launch("attention_prefill");
 }
 
@@ -872,6 +903,37 @@ FB_API int fb_attention_prefill(const void* q, long long q_stride, void* out, lo
     case 32: return launch_prefill<32>(p, q_blocks, stream);
     case 64: return launch_prefill<64>(p, q_blocks, stream);
     default: return launch_prefill<128>(p, q_blocks, stream);
+  }
+}
+
+// The same with a window that keeps the first tokens, a bias by distance and a
+// sink (see AttnParams): prompts of a mixer whose keys and values have one size.
+FB_API int fb_attention_prefill_masked(const void* q, long long q_stride, void* out,
+                                       long long out_stride, const int* cu_tokens,
+                                       const int* kv_lens, const int* page_table, int max_pages,
+                                       const void* k_cache, const void* v_cache,
+                                       long long page_stride, long long head_stride, int n_seqs,
+                                       int q_blocks, int A, int Kh, int D, float scale, int window,
+                                       int keep_first, int sink, float steep,
+                                       cudaStream_t stream) {
+  int rc = check_common("attention_prefill_masked", n_seqs, A, Kh, D, q_stride, out_stride, q,
+                        k_cache, v_cache, page_stride, head_stride);
+  if (rc) return rc;
+  FB_REQUIRE(window >= 0 && keep_first >= 0 && steep >= 0.f, "attention_prefill_masked: bad mask");
+  if (q_blocks <= 0) return 0;
+  AttnParams p{};
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.cu_tokens = cu_tokens; p.kv_lens = kv_lens; p.page_table = page_table; p.max_pages = max_pages;
+  p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.page_stride = page_stride; p.head_stride = head_stride;
+  p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E; p.splits = 1;
+  p.window = window; p.keep_first = keep_first; p.sink = sink ? 1 : 0; p.steep = steep;
+  switch (D) {
+    case 16: return launch_prefill<16, true>(p, q_blocks, stream);
+    case 32: return launch_prefill<32, true>(p, q_blocks, stream);
+    case 64: return launch_prefill<64, true>(p, q_blocks, stream);
+    default: return launch_prefill<128, true>(p, q_blocks, stream);
   }
 }
 

@@ -162,3 +162,262 @@ FB_API int fb_moe_experts_rows(const void* h, int dtype, const void* gate_up, co
 #undef FB_MOE_ROWS
   return fb_check_launch("moe_experts_rows");
 }
+
+// ===================================================================== grouped
+// Many (token, choice) pairs: pairs are sorted by expert on the device, so that
+// an expert's matrices are read once for all of its tokens.
+//
+//   fb_moe_sort       counts per expert, their running sums, and for every pair
+//                     its place in the expert-sorted order (`place[t * top + c]`)
+//                     with the inverse list `pair_at[place]`
+//   fb_moe_gather     x_sorted[place] = x[token of the pair]
+//   fb_moe_gate_up_grouped / fb_moe_down_grouped
+//                     the two products for a handful of tokens per expert: a
+//                     block owns (expert, a slice of weight rows), stages up to
+//                     CHUNK of the expert's input rows in shared memory and
+//                     streams its weight rows once per chunk (CUDA cores,
+//                     32-bit sums); the activation is the first one's epilogue
+//   fb_moe_glu        the activation alone, for products made elsewhere
+//   fb_moe_combine    out[t] = sum_c weight[t, c] * y_sorted[place[t, c]] in the
+//                     order of c, so the sum does not depend on the sorting
+namespace {
+constexpr int CHUNK = 8;  // input rows an expert's block holds at a time
+
+__global__ void moe_sort_kernel(const int* chosen, int n_pairs, int E, int* __restrict__ counts,
+                                int* __restrict__ starts, int* __restrict__ place,
+                                int* __restrict__ pair_at) {
+  fb_pdl_wait();
+  // one block; counts and starts live in shared memory (E <= 256)
+  __shared__ int cnt[256], start[257];
+  for (int e = threadIdx.x; e < 256; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = chosen[i];
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) { start[e] = at; at += cnt[e]; }
+    start[E] = at;
+  }
+  __syncthreads();
+  // thread e places the pairs of expert e in the order of their indices: a fixed order
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int at = start[e];
+    for (int i = 0; i < n_pairs; ++i)
+      if (chosen[i] == e) { place[i] = at; pair_at[at] = i; ++at; }
+    counts[e] = cnt[e];
+    starts[e] = start[e];
+  }
+  if (threadIdx.x == 0) starts[E] = start[E];
+  // pairs without a valid expert (never for finite logits) are put nowhere
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = chosen[i];
+    if (e < 0 || e >= E) place[i] = -1;
+  }
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* x, const int* pair_at, const int* starts, int E, int top,
+                                  T* __restrict__ out, int W) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int at = blockIdx.x;
+  if (at >= starts[E]) return;
+  const int t = pair_at[at] / top;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)at * W + i] = x[(size_t)t * W + i];
+}
+
+__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+
+template <typename TI, typename TO>
+__global__ void moe_glu_kernel(const TI* gu, TO* __restrict__ out, int ff, float limit, float alpha,
+                               const int* starts, int E) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const size_t row = blockIdx.x;
+  if ((int)row >= starts[E]) return;
+  for (int f = threadIdx.x; f < ff; f += blockDim.x)
+    out[row * ff + f] = fb_from_float<TO>(glu_act(fb_load_coherent<TI>(gu + row * 2 * ff + f),
+                                                  fb_load_coherent<TI>(gu + row * 2 * ff + ff + f),
+                                                  limit, alpha));
+}
+
+// 8 consecutive weights of a row as floats
+template <typename T>
+__device__ __forceinline__ void w8(const T* __restrict__ p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void w8<float>(const float* __restrict__ p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void w8<__nv_bfloat16>(const __nv_bfloat16* __restrict__ p,
+                                                  float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+// A block owns (expert e, weight rows [row0, row0 + rows)); K % 8 == 0 and the
+// weight rows 16-byte aligned (checked by the launcher). NR weight rows are
+// walked together by a warp: GATED walks a gate row and its up row (NR = 2).
+// xs: the chunk's input rows [CHUNK][K] as floats in shared memory.
+template <typename T, typename TX, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const int* starts,
+                   float* __restrict__ out, long long ldo, int K, int N, int rows_per_block,
+                   float limit, float alpha) {
+  fb_pdl_wait();
+  extern __shared__ float xs[];  // [CHUNK][K]
+  const int e = blockIdx.x;
+  const int begin = starts[e], end = starts[e + 1];
+  if (begin >= end) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int row0 = blockIdx.y * rows_per_block;
+  const int row1 = min(N, row0 + rows_per_block);
+  // GATED: w is [E][2N][K] (gate rows, then up rows), else [E][N][K]
+  const T* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+  for (int c0 = begin; c0 < end; c0 += CHUNK) {
+    const int nc = min(CHUNK, end - c0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nc * K; i += blockDim.x) {
+      const int r = i / K, k = i - r * K;
+      xs[r * K + k] = fb_load_coherent<TX>(x + (size_t)(c0 + r) * ldx + k);
+    }
+    __syncthreads();
+    for (int row = row0 + warp; row < row1; row += nwarps) {
+      float acc[CHUNK], acc2[CHUNK];
+#pragma unroll
+      for (int r = 0; r < CHUNK; ++r) acc[r] = acc2[r] = 0.f;
+      const T* wr = we + (size_t)row * K;
+      const T* wr2 = we + (size_t)(N + row) * K;
+      for (int k = lane * 8; k < K; k += 256) {
+        float a[8], b[8];
+        w8<T>(wr + k, a);
+        if (GATED) w8<T>(wr2 + k, b);
+#pragma unroll
+        for (int r = 0; r < CHUNK; ++r) {
+          if (r < nc) {
+            const float4 x0 = *reinterpret_cast<const float4*>(xs + r * K + k);
+            const float4 x1 = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
+            acc[r] = fmaf(a[0], x0.x, acc[r]); acc[r] = fmaf(a[1], x0.y, acc[r]);
+            acc[r] = fmaf(a[2], x0.z, acc[r]); acc[r] = fmaf(a[3], x0.w, acc[r]);
+            acc[r] = fmaf(a[4], x1.x, acc[r]); acc[r] = fmaf(a[5], x1.y, acc[r]);
+            acc[r] = fmaf(a[6], x1.z, acc[r]); acc[r] = fmaf(a[7], x1.w, acc[r]);
+            if (GATED) {
+              acc2[r] = fmaf(b[0], x0.x, acc2[r]); acc2[r] = fmaf(b[1], x0.y, acc2[r]);
+              acc2[r] = fmaf(b[2], x0.z, acc2[r]); acc2[r] = fmaf(b[3], x0.w, acc2[r]);
+              acc2[r] = fmaf(b[4], x1.x, acc2[r]); acc2[r] = fmaf(b[5], x1.y, acc2[r]);
+              acc2[r] = fmaf(b[6], x1.z, acc2[r]); acc2[r] = fmaf(b[7], x1.w, acc2[r]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < CHUNK; ++r) {
+        if (r < nc) {  // uniform over the warp
+          const float g = fb_warp_sum(acc[r]);
+          const float u = GATED ? fb_warp_sum(acc2[r]) : 0.f;
+          if (lane == 0)
+            out[(size_t)(c0 + r) * ldo + row] = GATED ? glu_act(g, u, limit, alpha) : g;
+        }
+      }
+    }
+  }
+}
+
+__global__ void moe_combine_kernel(const float* y, const int* place, const float* weights, int top,
+                                   float* __restrict__ out, int W) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float acc = 0.f;
+    for (int c = 0; c < top; ++c) {
+      const int at = place[t * top + c];
+      if (at >= 0) acc = fmaf(weights[t * top + c], __ldcg(y + (size_t)at * W + i), acc);
+    }
+    out[t * W + i] = acc;
+  }
+}
+}  // namespace
+
+FB_API int fb_moe_sort(const int* chosen, int n_pairs, int E, int* counts, int* starts, int* place,
+                       int* pair_at, cudaStream_t stream) {
+  FB_REQUIRE(n_pairs >= 0 && E > 0 && E <= 256, "moe_sort: %d experts (at most 256)", E);
+  fb_launch(moe_sort_kernel, dim3(1), dim3(256), 0, stream, chosen, n_pairs, E, counts, starts,
+            place, pair_at);
+  return fb_check_launch("moe_sort");
+}
+
+FB_API int fb_moe_gather(const void* x, int dtype, const int* pair_at, const int* starts, int E,
+                         int top, void* out, int n_pairs, int W, cudaStream_t stream) {
+  FB_REQUIRE(n_pairs >= 0 && W > 0 && top > 0, "moe_gather: bad sizes");
+  if (n_pairs == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, T_, (fb_launch(moe_gather_kernel<T_>, dim3(n_pairs), dim3(256), 0,
+      stream, (const T_*)x, pair_at, starts, E, top, (T_*)out, W)));
+  return fb_check_launch("moe_gather");
+}
+
+FB_API int fb_moe_glu(const void* gu, int in_dtype, void* out, int out_dtype, int n_pairs, int ff,
+                      float limit, float alpha, const int* starts, int E, cudaStream_t stream) {
+  FB_REQUIRE(n_pairs >= 0 && ff > 0, "moe_glu: bad sizes");
+  if (n_pairs == 0) return 0;
+  FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, TO, (fb_launch(
+      moe_glu_kernel<TI, TO>, dim3(n_pairs), dim3(256), 0, stream, (const TI*)gu, (TO*)out, ff,
+      limit, alpha, starts, E))));
+  return fb_check_launch("moe_glu");
+}
+
+// gated = 1: x rows in the weights' element type, w = gate_up [E, 2N, K], out = activations
+// gated = 0: x rows are float32 (the activations), w = down [E, N, K], out = products
+FB_API int fb_moe_grouped(int gated, const void* x, long long ldx, const void* w, int w_dtype,
+                          const int* starts, float* out, long long ldo, int E, int K, int N,
+                          float limit, float alpha, int sm_count, cudaStream_t stream) {
+  FB_REQUIRE(E > 0 && K > 0 && N > 0 && ldx >= K && ldo >= N, "moe_grouped: bad sizes");
+  FB_REQUIRE(K % 8 == 0 && ((uintptr_t)w % 16) == 0 && ldx % 4 == 0,
+             "moe_grouped: K = %d must be a multiple of 8 and the matrices 16-byte aligned", K);
+  const size_t smem = (size_t)CHUNK * K * 4;
+  FB_REQUIRE(smem <= 200 * 1024, "moe_grouped: %d input rows of %d do not fit shared memory",
+             CHUNK, K);
+  // row slices so that the experts in use cover the SMs a few times over
+  int slices = (4 * (sm_count > 0 ? sm_count : 148) + E - 1) / E;
+  int rows = (N + slices - 1) / slices;
+  rows = (rows + 7) / 8 * 8;
+  dim3 grid(E, (N + rows - 1) / rows);
+#define FB_MOE_GROUPED(T_, TX_, G_)                                                             \
+  do {                                                                                          \
+    static bool seen[64];                                                                       \
+    if (smem > 48 * 1024 && fb_first_use_on_device(seen))                                       \
+      cudaFuncSetAttribute(moe_grouped_kernel<T_, TX_, G_>,                                     \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);            \
+    fb_launch(moe_grouped_kernel<T_, TX_, G_>, grid, dim3(256), smem, stream, (const TX_*)x,    \
+              ldx, (const T_*)w, starts, out, ldo, K, N, rows, limit, alpha);                   \
+  } while (0)
+  if (gated) {
+    FB_DISPATCH_DTYPE(w_dtype, T_, FB_MOE_GROUPED(T_, T_, true));
+  } else {
+    FB_DISPATCH_DTYPE(w_dtype, T_, FB_MOE_GROUPED(T_, float, false));
+  }
+#undef FB_MOE_GROUPED
+  return fb_check_launch("moe_grouped");
+}
+
+FB_API int fb_moe_combine(const float* y, const int* place, const float* weights, int top,
+                          float* out, int T, int W, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && W > 0 && top > 0, "moe_combine: bad sizes");
+  if (T == 0) return 0;
+  fb_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, y, place, weights, top, out, W);
+  return fb_check_launch("moe_combine");
+}

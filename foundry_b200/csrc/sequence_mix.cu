@@ -159,21 +159,58 @@ struct ScanArgs {
   int H, rep, dim, vdim;
 };
 
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() {
+  asm volatile("cp.async.wait_group 1;" ::: "memory");
+}
+
+// The inputs of `tc` tokens at a time are brought into shared memory by
+// asynchronous copies (two buffers: the next tokens arrive while these are
+// worked), so the token-by-token loop waits for shared memory, not for L2.
+// Per token: q [dim] | k [dim] | g [dim] | v [the block's columns] | beta.
 template <int MODE, int KP>
-__global__ void __launch_bounds__(256) scan_kernel(ScanArgs a) {
+__global__ void __launch_bounds__(128) scan_kernel(ScanArgs a, int tc) {
   fb_pdl_wait();
   constexpr int COLS_W = 32 / KP;  // columns a warp holds
+  extern __shared__ float sbuf[];
   const int seq = blockIdx.x, h = blockIdx.y;
   const int start = a.cu_tokens[seq], n = a.cu_tokens[seq + 1] - start;
   if (n <= 0) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int part = lane / COLS_W;
-  const int j = (blockIdx.z * nwarps + warp) * COLS_W + lane % COLS_W;
+  const int cols_blk = nwarps * COLS_W;
+  const int col0 = blockIdx.z * cols_blk;
+  const int jl = warp * COLS_W + lane % COLS_W;  // column within the block
+  const int j = col0 + jl;
   const bool col = j < a.vdim;
   const int dim = a.dim, vdim = a.vdim;
   float* S = a.state + (long long)a.slots[seq] * a.state_stride + a.s_offset +
              (long long)h * dim * vdim;
   const long long qoff = (long long)(h / a.rep) * dim, goff = (long long)h * dim;
+  const int per_tok = 3 * dim + cols_blk + 1;
+
+  auto stage = [&](int buf, int t0, int nt) {
+    float* dst = sbuf + (size_t)buf * tc * per_tok;
+    for (int idx = threadIdx.x; idx < nt * per_tok; idx += blockDim.x) {
+      const int r = idx / per_tok, c = idx - r * per_tok;
+      const size_t t = (size_t)(t0 + r);
+      const float* src = nullptr;
+      if (c < dim) src = a.q + t * a.q_ld + qoff + c;
+      else if (c < 2 * dim) src = a.k + t * a.k_ld + qoff + (c - dim);
+      else if (c < 3 * dim) src = a.g + t * a.g_ld + goff + (c - 2 * dim);
+      else if (c < 3 * dim + cols_blk) {
+        if (col0 + (c - 3 * dim) < vdim) src = a.v + t * a.v_ld + (size_t)h * vdim + col0 + (c - 3 * dim);
+      } else if (MODE == 0) {
+        src = a.beta + t * a.beta_ld + h;
+      }
+      if (src != nullptr) cp_async4(dst + idx, src);
+      else dst[idx] = 0.f;
+    }
+  };
 
   float s[R], bonus[R];
 #pragma unroll
@@ -182,53 +219,56 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a) {
     s[i] = (col && row < dim) ? S[(size_t)row * vdim + j] : 0.f;
     bonus[i] = (MODE == 1 && row < dim) ? a.bonus[goff + row] : 0.f;
   }
-  float qn[R], kn[R], gn[R], vn = 0.f, bn = 0.f;
-  auto load = [&](int t) {
+  stage(0, start, min(tc, n));
+  cp_async_commit();
+  for (int c0 = 0; c0 < n; c0 += tc) {
+    const int buf = (c0 / tc) & 1, nt = min(tc, n - c0);
+    if (c0 + tc < n) stage(buf ^ 1, start + c0 + tc, min(tc, n - c0 - tc));
+    cp_async_commit();  // (an empty group when nothing follows: the count below stays right)
+    cp_async_wait_but_one();
+    __syncthreads();
+    const float* tok = sbuf + (size_t)buf * tc * per_tok;
+    for (int r = 0; r < nt; ++r, tok += per_tok) {
+      const float v = tok[3 * dim + jl];
+      float o = 0.f;
+      if (MODE == 0) {
+        float kv = 0.f;
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-      const int row = i * KP + part;
-      const bool ok = row < dim;
-      qn[i] = ok ? __ldcg(a.q + (size_t)t * a.q_ld + qoff + row) : 0.f;
-      kn[i] = ok ? __ldcg(a.k + (size_t)t * a.k_ld + qoff + row) : 0.f;
-      gn[i] = ok ? __ldcg(a.g + (size_t)t * a.g_ld + goff + row) : 0.f;
+        for (int i = 0; i < R; ++i) {
+          const int row = i * KP + part;
+          if (row < dim) {
+            s[i] *= tok[2 * dim + row];
+            kv = fmaf(s[i], tok[dim + row], kv);
+          }
+        }
+#pragma unroll
+        for (int off = COLS_W; off < 32; off <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
+        const float u = sigmoidf_(tok[3 * dim + cols_blk]) * (v - kv);
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int row = i * KP + part;
+          if (row < dim) {
+            s[i] = fmaf(tok[dim + row], u, s[i]);
+            o = fmaf(s[i], tok[row], o);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int row = i * KP + part;
+          if (row < dim) {
+            const float kvi = tok[dim + row] * v;
+            o = fmaf(tok[row], fmaf(bonus[i], kvi, s[i]), o);
+            s[i] = fmaf(tok[2 * dim + row], s[i], kvi);
+          }
+        }
+      }
+#pragma unroll
+      for (int off = COLS_W; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (col && part == 0)
+        a.out[(size_t)(start + c0 + r) * a.H * vdim + (size_t)h * vdim + j] = o;
     }
-    vn = col ? __ldcg(a.v + (size_t)t * a.v_ld + (size_t)h * vdim + j) : 0.f;
-    if (MODE == 0) bn = __ldcg(a.beta + (size_t)t * a.beta_ld + h);
-  };
-  load(start);
-  for (int t = start; t < start + n; ++t) {
-    float q[R], k[R], g[R];
-#pragma unroll
-    for (int i = 0; i < R; ++i) { q[i] = qn[i]; k[i] = kn[i]; g[i] = gn[i]; }
-    const float v = vn, braw = bn;
-    if (t + 1 < start + n) load(t + 1);  // the next token's loads fly while this one is worked
-    float o = 0.f;
-    if (MODE == 0) {
-      float kv = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        s[i] *= g[i];
-        kv = fmaf(s[i], k[i], kv);
-      }
-#pragma unroll
-      for (int off = COLS_W; off < 32; off <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
-      const float u = sigmoidf_(braw) * (v - kv);
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        s[i] = fmaf(k[i], u, s[i]);
-        o = fmaf(s[i], q[i], o);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const float kvi = k[i] * v;
-        o = fmaf(q[i], fmaf(bonus[i], kvi, s[i]), o);
-        s[i] = fmaf(g[i], s[i], kvi);
-      }
-    }
-#pragma unroll
-    for (int off = COLS_W; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-    if (col && part == 0) a.out[(size_t)t * a.H * vdim + (size_t)h * vdim + j] = o;
+    __syncthreads();  // the buffer is refilled by the next iteration's copies
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
@@ -356,10 +396,16 @@ FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* 
   const int warps_needed = (vdim + cols_w - 1) / cols_w;
   const int warps = warps_needed < 4 ? warps_needed : 4;
   dim3 grid(n_seqs, H, (warps_needed + warps - 1) / warps);
+  // tokens staged at a time: two buffers within the 48 KB that need no opt-in
+  const int per_tok = 3 * dim + warps * cols_w + 1;
+  int tc = 16;
+  while (tc > 1 && (size_t)2 * tc * per_tok * 4 > 48 * 1024) tc /= 2;
+  const size_t smem = (size_t)2 * tc * per_tok * 4;
+  FB_REQUIRE(smem <= 48 * 1024, "state_scan: a token's inputs (%d floats) do not fit", per_tok);
 #define FB_SCAN(KP)                                                                              \
   case KP:                                                                                       \
-    if (mode == 0) fb_launch(scan_kernel<0, KP>, grid, dim3(warps * 32), 0, stream, a);          \
-    else fb_launch(scan_kernel<1, KP>, grid, dim3(warps * 32), 0, stream, a);                    \
+    if (mode == 0) fb_launch(scan_kernel<0, KP>, grid, dim3(warps * 32), smem, stream, a, tc);   \
+    else fb_launch(scan_kernel<1, KP>, grid, dim3(warps * 32), smem, stream, a, tc);             \
     break;
   switch (kp) {
     FB_SCAN(1) FB_SCAN(2) FB_SCAN(4) FB_SCAN(8) FB_SCAN(16) FB_SCAN(32)

@@ -106,7 +106,8 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                       const int* __restrict__ page_table, int max_pages, const T* k_cache,
                       const T* v_cache, long long k_page, long long k_head, long long v_page,
-                      long long v_head, SinkMask mask, int H, int G, int D, int VD) {
+                      long long v_head, SinkMask mask, int H, int G, int D, int VD, int splits,
+                      float* __restrict__ partial) {
   fb_pdl_wait();
   __shared__ float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,15 +132,22 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
   const T* kbase = k_cache + (long long)g * k_head;
   const T* vbase = v_cache + (long long)g * v_head;
 
+  // With `splits` > 1 the visible keys (the kept ones, then the window's) are cut into
+  // that many runs; block z takes run z and leaves (max, sum, weighted values) for
+  // `attention_sink_merge_kernel`, which also adds the sink.
+  const int total = kept + (pos + 1 - lo);
+  const int i0 = (int)((long long)total * blockIdx.z / splits);
+  const int i1 = (int)((long long)total * (blockIdx.z + 1) / splits);
   // the sink is a key of score 0 without a value: it starts the running maximum and sum
-  float m = mask.sink ? 0.f : -INFINITY, l = mask.sink ? 1.f : 0.f;
+  const bool own_sink = mask.sink && splits == 1;
+  float m = own_sink ? 0.f : -INFINITY, l = own_sink ? 1.f : 0.f;
   float acc[MAX_D / 32];
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
 
   for (int range = 0; range < 2; ++range) {
-    const int begin = range == 0 ? 0 : lo;
-    const int end = range == 0 ? kept : pos + 1;  // exclusive
+    const int begin = range == 0 ? min(i0, kept) : lo + max(i0 - kept, 0);
+    const int end = range == 0 ? min(i1, kept) : lo + max(i1 - kept, 0);  // exclusive
     for (int j0 = begin; j0 < end; j0 += 32) {
       const int j = j0 + lane;
       float s = -INFINITY;
@@ -179,11 +187,59 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
       }
     }
   }
+  if (splits > 1) {
+    float* dst = partial + (((size_t)t * H + a) * splits + blockIdx.z) * (VD + 2);
+    if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < VD) dst[2 + d] = acc[i];
+    }
+    return;
+  }
   const float inv_l = 1.0f / l;
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) {
     const int d = lane + 32 * i;
     if (d < VD) o[d] = fb_from_float<T>(acc[i] * inv_l);
+  }
+}
+
+// One warp per (token, head): the runs' partial results become the output.
+template <typename T>
+__global__ void attention_sink_merge_kernel(const float* partial, T* __restrict__ out,
+                                            long long out_stride, const int* __restrict__ seq_of_token,
+                                            int H, int VD, int splits, int sink) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x, a = blockIdx.y * WARPS + warp;
+  if (a >= H || seq_of_token[t] < 0) return;  // padding rows were written by the first kernel
+  const float* src = partial + ((size_t)t * H + a) * splits * (VD + 2);
+  float M = sink ? 0.f : -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(src + (size_t)s * (VD + 2)));
+  float L = sink ? expf(-M) : 0.f;
+  float acc[MAX_D / 32];
+#pragma unroll
+  for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* ps = src + (size_t)s * (VD + 2);
+    const float ms = __ldcg(ps);
+    if (ms == -INFINITY) continue;  // an empty run
+    const float f = expf(ms - M);
+    L = fmaf(__ldcg(ps + 1), f, L);
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < VD) acc[i] = fmaf(__ldcg(ps + 2 + d), f, acc[i]);
+    }
+  }
+  const float inv = 1.0f / L;
+  T* o = out + (size_t)t * out_stride + (size_t)a * VD;
+#pragma unroll
+  for (int i = 0; i < MAX_D / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < VD) o[d] = fb_from_float<T>(acc[i] * inv);
   }
 }
 }  // namespace
@@ -213,7 +269,7 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
                              const void* v_cache, long long k_page, long long k_head,
                              long long v_page, long long v_head, int window, int keep_first,
                              int sink, float scale, float steep, int T, int H, int G, int D, int VD,
-                             cudaStream_t stream) {
+                             int splits, float* partial, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && H > 0 && G > 0 && D > 0 && VD > 0, "attention_sink: bad sizes");
   FB_REQUIRE(H % G == 0, "attention_sink: %d query heads are not a multiple of %d key-value heads",
              H, G);
@@ -222,12 +278,21 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
              "(value size %d)", D, MAX_D, VD);
   FB_REQUIRE(k_page % 8 == 0 && k_head % 8 == 0, "attention_sink: key rows are not 16-byte aligned");
   FB_REQUIRE(window >= 0 && keep_first >= 0 && max_pages > 0, "attention_sink: bad mask");
+  FB_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || partial != nullptr),
+             "attention_sink: %d runs need a workspace", splits);
   if (T == 0) return 0;
   SinkMask mask{window, keep_first, sink ? 1 : 0, scale, steep};
-  dim3 grid(T, (H + WARPS - 1) / WARPS);
+  dim3 grid(T, (H + WARPS - 1) / WARPS, splits);
   FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E>, dim3(grid), dim3(WARPS * 32), 0,
       stream, (const E*)q, q_stride, (E*)out, out_stride, positions, seq_of_token, page_table,
       max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head, v_page, v_head, mask, H, G,
-      D, VD)));
+      D, VD, splits, partial)));
+  if (splits > 1) {
+    int rc = fb_check_launch("attention_sink");
+    if (rc) return rc;
+    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_merge_kernel<E>,
+        dim3(T, (H + WARPS - 1) / WARPS), dim3(WARPS * 32), 0, stream, (const float*)partial,
+        (E*)out, out_stride, seq_of_token, H, VD, splits, sink ? 1 : 0)));
+  }
   return fb_check_launch("attention_sink");
 }

@@ -95,7 +95,11 @@ _SIGNATURES = {
                                c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_attention_sink": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
                           c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_int,
-                          c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                          c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                          c_void_p],
+    "fb_attention_prefill_masked": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int,
+                                    c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p],
     "fb_token_shift_mix": [c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "fb_state_tail_update": [c_void_p, c_int, c_ll, c_void_p, c_ll, c_ll, c_int, c_int, c_void_p,
@@ -113,6 +117,14 @@ _SIGNATURES = {
     "fb_moe_route": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "fb_moe_experts_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "fb_moe_sort": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "fb_moe_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                      c_void_p],
+    "fb_moe_glu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p,
+                   c_int, c_void_p],
+    "fb_moe_grouped": [c_int, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_int,
+                       c_int, c_int, c_float, c_float, c_int, c_void_p],
+    "fb_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
 }
 
 _FUNCS = {}
@@ -1592,21 +1604,52 @@ def _check_kv_pair(k_cache, v_cache, G, dim, vdim, dtype) -> None:
                               f"[pages, {G}, {PAGE}, {d}] with contiguous rows")
 
 
+SINK_ATTENTION_TC = _os.environ.get("FOUNDRY_B200_SINK_ATTENTION_TC", "1") != "0"
+SINK_DECODE_WARPS = 2400  # warps a single-token step's attention should come to
+
+
 def attention_sink(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache, v_cache, H: int,
                    G: int, dim: int, vdim: int, scale: float, window: int = 0, keep_first: int = 0,
                    sink: bool = False, steep: float = 0.0) -> torch.Tensor:
     """Causal attention of every token of the step over its sequence's cache,
-    with the mask, bias and sink of csrc/sink_attention.cu."""
+    with the mask, bias and sink of csrc/sink_attention.cu. Prompts in bfloat16
+    whose keys and values have one tensor-core head size run the masked form of
+    the tensor-core prompt kernel; everything else the CUDA-core kernel, whose
+    single-token steps cut every token's visible keys into runs."""
     T = q.shape[0]
+    window, keep_first = int(window or 0), int(keep_first or 0)
     _check_kv_pair(k_cache, v_cache, G, dim, vdim, q.dtype)
+    if (SINK_ATTENTION_TC and not ctx.is_decode and q.dtype == torch.bfloat16 and dim == vdim
+            and dim in FAST_HEAD_DIMS and H // G <= 16 and k_cache.stride() == v_cache.stride()
+            and _tc_attention_ok(q, out)):
+        q_blocks = ctx.query_blocks_bound
+        if q_blocks is None:
+            cu = ctx.cu_tokens_host
+            q_blocks = sum((cu[i + 1] - cu[i] + 63) // 64 for i in range(ctx.n_seqs))
+        _call("fb_attention_prefill_masked", _dev(q, "q", contiguous=False), _rows(q, "q"),
+              _dev(out, "out", contiguous=False), _rows(out, "out"),
+              _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.kv_lens, "kv_lens", torch.int32),
+              _dev(page_table, "page_table", torch.int32), page_table.shape[1],
+              k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
+              ctx.n_seqs, q_blocks, H, G, dim, float(scale), window, keep_first,
+              1 if sink else 0, float(steep), _stream())
+        return out
+    splits, partial = 1, 0
+    if ctx.is_decode and T > 0:
+        seen = ctx.max_kv_len if not window else min(ctx.max_kv_len, window + keep_first)
+        splits = max(1, min((seen + 63) // 64, SINK_DECODE_WARPS // max(1, T * H), 64))
+        if splits > 1:
+            partial = torch.empty(T * H * splits * (vdim + 2), dtype=torch.float32,
+                                  device=q.device).data_ptr()
     _call("fb_attention_sink", _dev(q, "q", contiguous=False), _rows(q, "q"),
           _dev(out, "out", q.dtype, contiguous=False), _rows(out, "out"), code_of(q.dtype),
           _dev(ctx.positions, "positions", torch.int32),
           _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1],
           k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
-          v_cache.stride(0), v_cache.stride(1), int(window or 0), int(keep_first or 0),
-          1 if sink else 0, float(scale), float(steep), T, H, G, dim, vdim, _stream())
+          v_cache.stride(0), v_cache.stride(1), window, keep_first,
+          1 if sink else 0, float(scale), float(steep), T, H, G, dim, vdim, splits, partial,
+          _stream())
     return out
 
 
@@ -1746,4 +1789,74 @@ def moe_experts_rows(h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
           _dev(down, "down"), _dev(chosen, "chosen", torch.int32),
           _dev(weights, "weights", torch.float32), _dev(out, "out", torch.float32), T, W,
           two_ff // 2, chosen.shape[1], E, float(limit), float(alpha), _stream())
+    return out
+
+
+class ExpertOrder:
+    """The (token, choice) pairs of a step sorted by expert, on the device:
+    `starts` [E + 1] running sums of the experts' pair counts, `place` [T, top]
+    each pair's row in the sorted order (-1: none), `pair_at` the inverse."""
+
+    def __init__(self, chosen: torch.Tensor, experts: int):
+        T, top = chosen.shape
+        dev = chosen.device
+        self.T, self.top, self.experts, self.pairs = T, top, experts, T * top
+        self.counts = torch.empty(experts, dtype=torch.int32, device=dev)
+        self.starts = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+        self.place = torch.empty((T, top), dtype=torch.int32, device=dev)
+        self.pair_at = torch.empty(T * top, dtype=torch.int32, device=dev)
+        _call("fb_moe_sort", _dev(chosen, "chosen", torch.int32), self.pairs, experts,
+              self.counts.data_ptr(), self.starts.data_ptr(), self.place.data_ptr(),
+              self.pair_at.data_ptr(), _stream())
+
+
+def moe_gather(x: torch.Tensor, order: ExpertOrder) -> torch.Tensor:
+    """The input row of every pair, in the expert-sorted order."""
+    out = torch.empty((order.pairs, x.shape[1]), dtype=x.dtype, device=x.device)
+    _call("fb_moe_gather", _dev(x, "x"), code_of(x.dtype), order.pair_at.data_ptr(),
+          order.starts.data_ptr(), order.experts, order.top, out.data_ptr(), order.pairs,
+          x.shape[1], _stream())
+    return out
+
+
+def moe_glu(gate_up: torch.Tensor, out: torch.Tensor, order: ExpertOrder, limit: float,
+            alpha: float) -> torch.Tensor:
+    """out = min(g, limit) * sigmoid(alpha min(g, limit)) * (clamp(u, +-limit) + 1) for rows
+    [g | u] of `gate_up`."""
+    n, two_ff = gate_up.shape
+    _call("fb_moe_glu", _dev(gate_up, "gate_up"), code_of(gate_up.dtype), _dev(out, "out"),
+          code_of(out.dtype), n, two_ff // 2, float(limit), float(alpha), order.starts.data_ptr(),
+          order.experts, _stream())
+    return out
+
+
+MOE_GROUPED_CHUNK = 8  # CHUNK in csrc/moe.cu
+
+
+def moe_grouped_fits(K: int) -> bool:
+    return K % 8 == 0 and MOE_GROUPED_CHUNK * K * 4 <= 200 * 1024
+
+
+def moe_grouped(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: bool,
+                limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+    """For every expert, its sorted rows of `x` times its matrix in `w` ([E, N, K],
+    or [E, 2N, K] gate rows then up rows when `gated`, which also applies the
+    activation); float32 out [pairs, N]."""
+    E, rows, K = w.shape
+    N = rows // 2 if gated else rows
+    out = torch.empty((order.pairs, N), dtype=torch.float32, device=x.device)
+    if order.pairs == 0:
+        return out
+    want = w.dtype if gated else torch.float32
+    _call("fb_moe_grouped", 1 if gated else 0, _dev(x, "x", want), x.stride(0), _dev(w, "w"),
+          code_of(w.dtype), order.starts.data_ptr(), out.data_ptr(), N, E, K, N, float(limit),
+          float(alpha), sm_count(), _stream())
+    return out
+
+
+def moe_combine(y: torch.Tensor, order: ExpertOrder, weights: torch.Tensor,
+                out: torch.Tensor) -> torch.Tensor:
+    _call("fb_moe_combine", _dev(y, "y", torch.float32), order.place.data_ptr(),
+          _dev(weights, "weights", torch.float32), order.top, _dev(out, "out", torch.float32),
+          order.T, out.shape[1], _stream())
     return out

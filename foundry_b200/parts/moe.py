@@ -19,6 +19,7 @@ import torch
 from ..kernels import ops
 from ..weights.loader import ExpectedTensor
 from .base import Fetch, Part, register_feed_forward
+from .linear import matmul_nt
 from .products import product_f32
 
 
@@ -64,5 +65,37 @@ class RoutedExperts(Part):
         weights = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
         ops.moe_route(z, self.router_bias, self.top, chosen, weights)
         out = torch.empty((T, self.width), dtype=torch.float32, device=x.device)
-        return ops.moe_experts_rows(x, self.gate_up, self.down, chosen, weights, out, self.limit,
-                                    self.alpha)
+        if not (ops.moe_grouped_fits(self.width) and ops.moe_grouped_fits(self.ff)):
+            # sizes the grouped kernels do not take: every token streams its own experts
+            return ops.moe_experts_rows(x, self.gate_up, self.down, chosen, weights, out,
+                                        self.limit, self.alpha)
+        order = ops.ExpertOrder(chosen, self.experts)
+        rows = ops.moe_gather(x, order)
+        if T >= self.LIBRARY_ROWS and getattr(ctx, "cu_tokens_host", None) is not None:
+            y = self._per_expert_products(rows, order)
+        else:
+            act = ops.moe_grouped(rows, self.gate_up, order, True, self.limit, self.alpha)
+            y = ops.moe_grouped(act, self.down, order, False)
+        return ops.moe_combine(y, order, weights, out)
+
+    # From this many tokens on, a step that is launched plainly (its context has the
+    # host copies; such a step is never captured) runs every expert's rows through
+    # the tensor-core products, which needs the experts' counts on the host.
+    LIBRARY_ROWS = 128
+
+    def _per_expert_products(self, rows, order):
+        starts = order.starts.tolist()  # waits for the routing
+        pairs, dev = order.pairs, rows.device
+        gate_up = torch.empty((pairs, 2 * self.ff), dtype=torch.float32, device=dev)
+        for e in range(self.experts):
+            a, b = starts[e], starts[e + 1]
+            if b > a:
+                matmul_nt(rows[a:b], self.gate_up[e], gate_up[a:b])
+        act = torch.empty((pairs, self.ff), dtype=rows.dtype, device=dev)
+        ops.moe_glu(gate_up, act, order, self.limit, self.alpha)
+        y = torch.empty((pairs, self.width), dtype=torch.float32, device=dev)
+        for e in range(self.experts):
+            a, b = starts[e], starts[e + 1]
+            if b > a:
+                matmul_nt(act[a:b], self.down[e], y[a:b])
+        return y

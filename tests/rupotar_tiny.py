@@ -1,7 +1,7 @@
 """Small Rupotar configurations for the tests, and random weights for them.
 
 The two differ from each other in every size: widths, head counts and
-groupings, key and value sizes (unequal), taps, ranks, experts and how many are
+groupings, key and value sizes (unequal in one, equal in the other), taps, ranks, experts and how many are
 chosen (also one), windows (shorter than a page, longer than a page, none),
 kept first tokens (none, some), layers without feed-forward, the order of the
 mixers, a loop of three passes over the first layers, and no loop.
@@ -37,7 +37,7 @@ CONFIGS = {
              "mlp": {"kind": "moe", "expert": {"ff": 24, "limit": 2.5},
                      "router": {"experts": 3, "top": 1}}},
             {"type": "attention",
-             "mixer": {"heads": 4, "kv_heads": 4, "dim": 8, "vdim": 16, "scale": 0.5,
+             "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 16, "scale": 0.5,
                        "mask": {"size": 70, "keep_first": 0}},
              "mlp": None},
             {"type": "wkv", "mixer": {"heads": 2, "dim": 40},

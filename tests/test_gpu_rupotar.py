@@ -178,8 +178,9 @@ EDGES = [  # (query position, marker position, whether the window of 70 with 3 k
 ]
 
 
+@pytest.mark.parametrize("W", [8, 16])  # 16: a head size of the tensor-core prompt kernel
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_attention_at_the_edges_of_window_kept_tokens_and_pages(dtype):
+def test_attention_at_the_edges_of_window_kept_tokens_and_pages(dtype, W):
     """A crafted mixer (identity projections) in which one key dominates one
     query: just inside and just outside the window, at the first tokens that
     are kept and the next ones, on both sides of a page border, far back; as
@@ -187,20 +188,19 @@ def test_attention_at_the_edges_of_window_kept_tokens_and_pages(dtype):
     from foundry_b200.cache import SequenceCache
     from foundry_b200.parts import MIXERS
     from foundry_b200.config.spec import PartSpec
-    W = 8
-    m = {"heads": 1, "kv_heads": 1, "dim": W, "vdim": W, "scale": 3.0,
+    m = {"heads": 1, "kv_heads": 1, "dim": W, "vdim": W, "scale": 3.0 * 8 / W,
          "mask": {"size": 70, "keep_first": 3}}
-    lower = torch.diag(torch.tensor([1.0] * 4 + [0.0] * 4))  # queries and keys read the lower half
-    upper = torch.diag(torch.tensor([0.0] * 4 + [1.0] * 4))  # values the upper half of a row
+    lower = torch.diag(torch.tensor([1.0] * 4 + [0.0] * (W - 4)))  # queries and keys read the first four
+    upper = torch.diag(torch.tensor([0.0] * 4 + [1.0] * (W - 4)))  # values the rest of a row
     weights = {"a.q": lower, "a.k": lower, "a.v": upper, "a.o": torch.eye(W),
                "a.q.norm": torch.ones(W), "a.k.norm": torch.ones(W)}
     part = MIXERS.build(PartSpec("sink_window_attention", {
-        "width": W, "heads": 1, "kv_heads": 1, "dim": W, "vdim": W, "scale": 3.0, "eps": 1e-6,
+        "width": W, "heads": 1, "kv_heads": 1, "dim": W, "vdim": W, "scale": 3.0 * 8 / W, "eps": 1e-6,
         "window": 70, "keep_first": 3, "steep": 8.0, "sink": True}), dtype=dtype, device=DEV)
     part.load("a", lambda n: weights[n].to(DEV).to(dtype if weights[n].dim() > 1 else torch.float32))
     cache = SequenceCache({0: part.cache_request()}, 4096, 4, dtype, DEV)
     for query_at, marker_at, shown in EDGES:
-        x = edge_case_inputs(query_at, marker_at)
+        x = edge_case_inputs(query_at, marker_at, W)
         want = plain.sink_attention(m, double(weights), "a", x.double(), 1e-6)[-1]
         # the plain implementation itself must tell the two kinds of case apart
         assert (float(want[4:].mean()) > 0.3) == shown, (query_at, marker_at)
