@@ -247,6 +247,112 @@ def workload_point(name: str, preset_name: str, prompts: int, longest: int, seed
     }
 
 
+def kernel_table(engine, steps_fn) -> dict:
+    """{kernel: {"n": launches, "us": device time}} of the steps `steps_fn` runs,
+    every launch bracketed by CUDA events (plain launches, no graphs); the
+    products' shape tags are dropped so that a kind of kernel is one row."""
+    import torch
+    from foundry_b200.kernels import ops
+    graphs = engine.use_graphs
+    engine.use_graphs = False
+    steps_fn()  # once untimed: allocations, first-use set-up
+    torch.cuda.synchronize()
+    ops.PROFILER.start("kernels")
+    steps_fn()
+    torch.cuda.synchronize()
+    taken = ops.PROFILER.take()
+    ops.PROFILER.start(None)
+    engine.use_graphs = graphs
+    rows = {}
+    for key, entry in taken.get("kernels", {}).items():
+        kind = key.split(" ")[0]
+        row = rows.setdefault(kind, {"n": 0, "us": 0.0})
+        row["n"] += entry.get("dispatch_count", 0)
+        row["us"] += entry.get("gpu_ns", 0.0) / 1e3
+    return {k: {"n": v["n"], "us": round(v["us"], 1)} for k, v in
+            sorted(rows.items(), key=lambda kv: -kv[1]["us"])}
+
+
+def design_point(preset_name: str, batch: int, context: int, prompt_tokens: int, steps: int,
+                 warmup: int) -> dict:
+    """Prefill (one prompt of `prompt_tokens` in one step) and decode (`batch`
+    sequences, one token each, around `context` tokens of context) of one named
+    configuration with random weights, device-timed; with the per-kernel device
+    times of one prompt step and one single-token step."""
+    import torch
+    from foundry_b200.bench import SplitMix64, token_rows
+    from foundry_b200.bench.presets import preset
+    from foundry_b200.engine import Engine, SequenceStep
+    doc = preset(preset_name)
+    vocab = int(doc.get("vocab_size", doc.get("vocab")))
+    engine = Engine.from_random(doc, seed=0, dtype="bfloat16", max_tokens=(batch + 1) * (context + 256),
+                                max_slots=batch + 1, norm_std=0.0)
+    prompt = token_rows(SplitMix64(1), 1, prompt_tokens, vocab)[0]
+    times = []
+    for it in range(3 + 5):
+        slot = engine.open_sequence()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.step([SequenceStep(slot, prompt, [prompt_tokens - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        engine.close_sequence(slot)
+        if it >= 3:
+            times.append(a.elapsed_time(b))
+    prefill_ms = sorted(times)[len(times) // 2]
+
+    def one_prompt():
+        slot = engine.open_sequence()
+        engine.step([SequenceStep(slot, prompt, [prompt_tokens - 1])])
+        engine.close_sequence(slot)
+    prefill_kernels = kernel_table(engine, one_prompt)
+
+    rows = token_rows(SplitMix64(2), batch, context, vocab)
+    slots = [engine.open_sequence() for _ in range(batch)]
+    first = max(1, context - (3 * steps + warmup) // 2)
+    for start in range(0, first, 1024):
+        engine.step([SequenceStep(s, r[start:min(first, start + 1024)], []) for s, r in zip(slots, rows)])
+    blocks, launches, _ = time_decode(engine, slots, steps, warmup, 3)
+    ms, mean_ctx = median_block(blocks)
+
+    def one_token():
+        engine.step([SequenceStep(s, [1], [0]) for s in slots])
+    decode_kernels = kernel_table(engine, one_token)
+    weight_bytes = engine.model.weight_bytes_read_per_step()
+    cache_bytes = engine.cache.bytes_per_token() * sum(mean_ctx)
+    state_bytes = sum(int(rows_.numel() // rows_.shape[0]) * rows_.element_size() * 2 * batch
+                      for rows_ in engine.cache.state.values())
+    for s in slots:
+        engine.close_sequence(s)
+    del engine
+    torch.cuda.empty_cache()
+    return {"model": preset_name, "batch": batch, "context": sum(mean_ctx) / len(mean_ctx),
+            "prefill": {"tokens": prompt_tokens, "ms": prefill_ms,
+                        "tokens_per_s": prompt_tokens / (prefill_ms * 1e-3), "kernels": prefill_kernels},
+            "decode": {"ms_per_step": ms, "tokens_per_s": batch / (ms * 1e-3), "gpu_launches": launches,
+                       "weight_bytes_all_experts": weight_bytes, "cache_bytes": int(cache_bytes),
+                       "state_bytes_read_and_written": state_bytes, "kernels": decode_kernels}}
+
+
+def run_design(args) -> dict:
+    """`--design rupotar`: Rupotar stacks of real layer sizes beside Llama stacks of
+    the same width, heads, feed-forward width, depth and vocabulary."""
+    hbm_gbs, tflops_burst, _, source = peaks()
+    out = {"design": args.design, "dtype": "bf16", "n_gpus": 1,
+           "data": "synthetic: random token ids (SplitMix64), random-init weights",
+           "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops_burst, "of": source}, "sizes": {}}
+    sampler = ClockSampler()
+    sampler.start()
+    for size in args.sizes.split(","):
+        out["sizes"][size] = {
+            name: design_point(f"{name}-{size}", args.batch, args.design_context, PREFILL_TOKENS,
+                               max(8, args.steps // 4), args.warmup)
+            for name in (args.design, "llama")}
+    out["clocks"] = sampler.stop()
+    return out
+
+
 def run(args) -> dict:
     import torch
     from foundry_b200.bench import SplitMix64, token_rows
@@ -392,6 +498,14 @@ def main() -> int:
                         help="leave out the 1B and 8B workload points")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch decode kernels one by one (for profilers)")
+    parser.add_argument("--design", default=None, choices=["rupotar"],
+                        help="instead of the default workload: stacks of this design at real layer "
+                             "sizes beside Llama stacks of equal size (prefill and decode "
+                             "throughput, per-kernel device times)")
+    parser.add_argument("--sizes", default="1b-layers,3b-layers",
+                        help="with --design: the size presets to run, with commas between them")
+    parser.add_argument("--design-context", type=int, default=2048,
+                        help="with --design: tokens of context around which decoding is timed")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -403,6 +517,9 @@ def main() -> int:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not built")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.design:
+        print(json.dumps(run_design(args)))
+        return 0
     print(json.dumps(run(args)))
     return 0
 

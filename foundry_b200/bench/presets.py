@@ -20,7 +20,36 @@ def _llama(layers, hidden, heads, kv_heads, head_dim, intermediate, vocab, facto
             "max_position_embeddings": max_positions}
 
 
+def _rupotar(layers, width, heads, kv_heads, dim, ff, vocab, window=1024, keep_first=4,
+             experts=16, top=2, rank=64, taps=4, loop=None) -> Dict:
+    """A Rupotar stack of real layer sizes: the three mixers in turn (attention,
+    wkv, channel_delta), dense and routed feed-forwards alternating (an expert a
+    quarter as wide as the dense one)."""
+    stack = []
+    for i in range(layers):
+        kind = ("attention", "wkv", "channel_delta")[i % 3]
+        if kind == "attention":
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                     "scale": dim ** -0.5, "mask": {"size": window, "keep_first": keep_first}}
+        elif kind == "wkv":
+            mixer = {"heads": heads, "dim": dim, "decay_rank": rank}
+        else:
+            mixer = {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": taps,
+                     "decay_rank": rank, "gate_rank": rank}
+        mlp = {"kind": "dense", "ff": ff} if i % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0},
+             "router": {"experts": experts, "top": top}}
+        stack.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Rupotar", "vocab": vocab, "width": width,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": stack, "loop": loop}
+
+
 PRESETS: Dict[str, Dict] = {
+    # six layers of the 1B and 3B layer sizes, as Rupotar and as Llama, for side-by-side timing
+    "rupotar-1b-layers": _rupotar(6, 2048, 32, 8, 64, 8192, 32000),
+    "rupotar-3b-layers": _rupotar(6, 3072, 24, 8, 128, 8192, 32000),
+    "llama-1b-layers": _llama(6, 2048, 32, 8, 64, 8192, 32000, None, False),
+    "llama-3b-layers": _llama(6, 3072, 24, 8, 128, 8192, 32000, None, False),
     "llama-3.2-1b": _llama(16, 2048, 32, 8, 64, 8192, 128256, 32.0, True),
     "llama-3.2-3b": _llama(28, 3072, 24, 8, 128, 8192, 128256, 32.0, True),
     "llama-3.1-8b": _llama(32, 4096, 32, 8, 128, 14336, 128256, 8.0, False),

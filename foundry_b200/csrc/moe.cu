@@ -202,13 +202,23 @@ __global__ void moe_sort_kernel(const int* chosen, int n_pairs, int E, int* __re
     start[E] = at;
   }
   __syncthreads();
-  // thread e places the pairs of expert e in the order of their indices: a fixed order
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+  // a warp places the pairs of an expert in the order of their indices (a fixed
+  // order): 32 pairs at a time, each lane's place from a ballot of the matching lanes
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
     int at = start[e];
-    for (int i = 0; i < n_pairs; ++i)
-      if (chosen[i] == e) { place[i] = at; pair_at[at] = i; ++at; }
-    counts[e] = cnt[e];
-    starts[e] = start[e];
+    for (int base = 0; base < n_pairs; base += 32) {
+      const int i = base + lane;
+      const bool mine = i < n_pairs && chosen[i] == e;
+      const unsigned hits = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int where = at + __popc(hits & ((1u << lane) - 1u));
+        place[i] = where;
+        pair_at[where] = i;
+      }
+      at += __popc(hits);
+    }
+    if (lane == 0) { counts[e] = cnt[e]; starts[e] = start[e]; }
   }
   if (threadIdx.x == 0) starts[E] = start[E];
   // pairs without a valid expert (never for finite logits) are put nowhere
@@ -274,7 +284,7 @@ __device__ __forceinline__ void w8<__nv_bfloat16>(const __nv_bfloat16* __restric
 // walked together by a warp: GATED walks a gate row and its up row (NR = 2).
 // xs: the chunk's input rows [CHUNK][K] as floats in shared memory.
 template <typename T, typename TX, bool GATED>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const int* starts,
                    float* __restrict__ out, long long ldo, int K, int N, int rows_per_block,
                    float limit, float alpha) {
@@ -302,24 +312,36 @@ moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const in
       for (int r = 0; r < CHUNK; ++r) acc[r] = acc2[r] = 0.f;
       const T* wr = we + (size_t)row * K;
       const T* wr2 = we + (size_t)(N + row) * K;
-      for (int k = lane * 8; k < K; k += 256) {
-        float a[8], b[8];
-        w8<T>(wr + k, a);
-        if (GATED) w8<T>(wr2 + k, b);
+      // two steps of 256 weights at a time: their loads are all issued before the sums
+      for (int k0 = lane * 8; k0 < K; k0 += 512) {
+        float a[2][8], b[2][8];
 #pragma unroll
-        for (int r = 0; r < CHUNK; ++r) {
-          if (r < nc) {
-            const float4 x0 = *reinterpret_cast<const float4*>(xs + r * K + k);
-            const float4 x1 = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
-            acc[r] = fmaf(a[0], x0.x, acc[r]); acc[r] = fmaf(a[1], x0.y, acc[r]);
-            acc[r] = fmaf(a[2], x0.z, acc[r]); acc[r] = fmaf(a[3], x0.w, acc[r]);
-            acc[r] = fmaf(a[4], x1.x, acc[r]); acc[r] = fmaf(a[5], x1.y, acc[r]);
-            acc[r] = fmaf(a[6], x1.z, acc[r]); acc[r] = fmaf(a[7], x1.w, acc[r]);
-            if (GATED) {
-              acc2[r] = fmaf(b[0], x0.x, acc2[r]); acc2[r] = fmaf(b[1], x0.y, acc2[r]);
-              acc2[r] = fmaf(b[2], x0.z, acc2[r]); acc2[r] = fmaf(b[3], x0.w, acc2[r]);
-              acc2[r] = fmaf(b[4], x1.x, acc2[r]); acc2[r] = fmaf(b[5], x1.y, acc2[r]);
-              acc2[r] = fmaf(b[6], x1.z, acc2[r]); acc2[r] = fmaf(b[7], x1.w, acc2[r]);
+        for (int u = 0; u < 2; ++u) {
+          if (k0 + u * 256 < K) {
+            w8<T>(wr + k0 + u * 256, a[u]);
+            if (GATED) w8<T>(wr2 + k0 + u * 256, b[u]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int k = k0 + u * 256;
+          if (k < K) {
+#pragma unroll
+            for (int r = 0; r < CHUNK; ++r) {
+              if (r < nc) {
+                const float4 x0 = *reinterpret_cast<const float4*>(xs + r * K + k);
+                const float4 x1 = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
+                acc[r] = fmaf(a[u][0], x0.x, acc[r]); acc[r] = fmaf(a[u][1], x0.y, acc[r]);
+                acc[r] = fmaf(a[u][2], x0.z, acc[r]); acc[r] = fmaf(a[u][3], x0.w, acc[r]);
+                acc[r] = fmaf(a[u][4], x1.x, acc[r]); acc[r] = fmaf(a[u][5], x1.y, acc[r]);
+                acc[r] = fmaf(a[u][6], x1.z, acc[r]); acc[r] = fmaf(a[u][7], x1.w, acc[r]);
+                if (GATED) {
+                  acc2[r] = fmaf(b[u][0], x0.x, acc2[r]); acc2[r] = fmaf(b[u][1], x0.y, acc2[r]);
+                  acc2[r] = fmaf(b[u][2], x0.z, acc2[r]); acc2[r] = fmaf(b[u][3], x0.w, acc2[r]);
+                  acc2[r] = fmaf(b[u][4], x1.x, acc2[r]); acc2[r] = fmaf(b[u][5], x1.y, acc2[r]);
+                  acc2[r] = fmaf(b[u][6], x1.z, acc2[r]); acc2[r] = fmaf(b[u][7], x1.w, acc2[r]);
+                }
+              }
             }
           }
         }
@@ -392,7 +414,7 @@ FB_API int fb_moe_grouped(int gated, const void* x, long long ldx, const void* w
   FB_REQUIRE(smem <= 200 * 1024, "moe_grouped: %d input rows of %d do not fit shared memory",
              CHUNK, K);
   // row slices so that the experts in use cover the SMs a few times over
-  int slices = (4 * (sm_count > 0 ? sm_count : 148) + E - 1) / E;
+  int slices = (6 * (sm_count > 0 ? sm_count : 148) + E - 1) / E;
   int rows = (N + slices - 1) / slices;
   rows = (rows + 7) / 8 * 8;
   dim3 grid(E, (N + rows - 1) / rows);

@@ -7,8 +7,8 @@
 //   o = (S + diag(b) k v^T)^T r;  S <- diag(w) S + k v^T
 //
 // Both recurrences act on the columns of S independently, so a thread owns a
-// slice of one column in registers (16 rows at most, the key rows dealt out
-// over KP lanes) and columns are spread over lanes, warps and blocks. A step
+// slice of one column in registers (16 consecutive key rows at most, a column
+// shared by KP lanes) and columns are spread over lanes, warps and blocks. A step
 // is two dot products over the key rows, finished by shuffles among the KP
 // lanes of a column. The state is 32-bit and lives in the sequence's state row
 // between steps; every sequence of the step is walked by its own blocks from
@@ -171,12 +171,14 @@ __device__ __forceinline__ void cp_async_wait_but_one() {
 // The inputs of `tc` tokens at a time are brought into shared memory by
 // asynchronous copies (two buffers: the next tokens arrive while these are
 // worked), so the token-by-token loop waits for shared memory, not for L2.
-// Per token: q [dim] | k [dim] | g [dim] | v [the block's columns] | beta.
+// Per token: q [dimp] | k [dimp] | g [dimp] | v [the block's columns] | beta | padding,
+// dimp = KP * rp the key rows padded so that lane group `part` holds the rp
+// consecutive rows part * rp .. (a multiple of 4: they are read as float4).
 template <int MODE, int KP>
-__global__ void __launch_bounds__(128) scan_kernel(ScanArgs a, int tc) {
+__global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc, int rp) {
   fb_pdl_wait();
   constexpr int COLS_W = 32 / KP;  // columns a warp holds
-  extern __shared__ float sbuf[];
+  extern __shared__ __align__(16) float sbuf[];
   const int seq = blockIdx.x, h = blockIdx.y;
   const int start = a.cu_tokens[seq], n = a.cu_tokens[seq + 1] - start;
   if (n <= 0) return;
@@ -188,36 +190,61 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs a, int tc) {
   const int j = col0 + jl;
   const bool col = j < a.vdim;
   const int dim = a.dim, vdim = a.vdim;
+  const int dimp = KP * rp;
   float* S = a.state + (long long)a.slots[seq] * a.state_stride + a.s_offset +
              (long long)h * dim * vdim;
   const long long qoff = (long long)(h / a.rep) * dim, goff = (long long)h * dim;
-  const int per_tok = 3 * dim + cols_blk + 1;
+  const int per_tok = (3 * dimp + cols_blk + 1 + 3) / 4 * 4;
+  const int row0 = part * rp;  // this thread's first key row
 
+  // what a thread copies is the same for every token: its elements of a token's record
+  // are found once (at most four a thread), then only the token's row offset changes
+  constexpr int MINE = 8;
+  const float* src0[MINE];
+  long long ld[MINE];
+  int at[MINE];
+#pragma unroll
+  for (int e = 0; e < MINE; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    const float* src = nullptr;
+    long long step = 0;
+    if (c < 3 * dimp) {
+      const int which = c / dimp, row = c - which * dimp;
+      if (row < dim) {
+        src = which == 0 ? a.q + qoff + row : which == 1 ? a.k + qoff + row : a.g + goff + row;
+        step = which == 0 ? a.q_ld : which == 1 ? a.k_ld : a.g_ld;
+      }
+    } else if (c < 3 * dimp + cols_blk) {
+      if (col0 + (c - 3 * dimp) < vdim) {
+        src = a.v + (size_t)h * vdim + col0 + (c - 3 * dimp);
+        step = a.v_ld;
+      }
+    } else if (MODE == 0 && c == 3 * dimp + cols_blk) {
+      src = a.beta + h;
+      step = a.beta_ld;
+    }
+    src0[e] = src; ld[e] = step; at[e] = c < per_tok ? c : -1;
+  }
   auto stage = [&](int buf, int t0, int nt) {
     float* dst = sbuf + (size_t)buf * tc * per_tok;
-    for (int idx = threadIdx.x; idx < nt * per_tok; idx += blockDim.x) {
-      const int r = idx / per_tok, c = idx - r * per_tok;
-      const size_t t = (size_t)(t0 + r);
-      const float* src = nullptr;
-      if (c < dim) src = a.q + t * a.q_ld + qoff + c;
-      else if (c < 2 * dim) src = a.k + t * a.k_ld + qoff + (c - dim);
-      else if (c < 3 * dim) src = a.g + t * a.g_ld + goff + (c - 2 * dim);
-      else if (c < 3 * dim + cols_blk) {
-        if (col0 + (c - 3 * dim) < vdim) src = a.v + t * a.v_ld + (size_t)h * vdim + col0 + (c - 3 * dim);
-      } else if (MODE == 0) {
-        src = a.beta + t * a.beta_ld + h;
+    for (int r = 0; r < nt; ++r) {
+#pragma unroll
+      for (int e = 0; e < MINE; ++e) {
+        if (at[e] >= 0) {
+          if (src0[e] != nullptr) cp_async4(dst + r * per_tok + at[e], src0[e] + (size_t)(t0 + r) * ld[e]);
+          else dst[r * per_tok + at[e]] = 0.f;
+        }
       }
-      if (src != nullptr) cp_async4(dst + idx, src);
-      else dst[idx] = 0.f;
     }
   };
 
   float s[R], bonus[R];
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int row = i * KP + part;
-    s[i] = (col && row < dim) ? S[(size_t)row * vdim + j] : 0.f;
-    bonus[i] = (MODE == 1 && row < dim) ? a.bonus[goff + row] : 0.f;
+    const int row = row0 + i;
+    const bool ok = i < rp && row < dim;
+    s[i] = (col && ok) ? S[(size_t)row * vdim + j] : 0.f;
+    bonus[i] = (MODE == 1 && ok) ? a.bonus[goff + row] : 0.f;
   }
   stage(0, start, min(tc, n));
   cp_async_commit();
@@ -229,40 +256,52 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs a, int tc) {
     __syncthreads();
     const float* tok = sbuf + (size_t)buf * tc * per_tok;
     for (int r = 0; r < nt; ++r, tok += per_tok) {
-      const float v = tok[3 * dim + jl];
-      float o = 0.f;
+      const float v = tok[3 * dimp + jl];
+      const float4* q4 = reinterpret_cast<const float4*>(tok + row0);
+      const float4* k4 = reinterpret_cast<const float4*>(tok + dimp + row0);
+      const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * dimp + row0);
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};  // four sums side by side: short dependent chains
       if (MODE == 0) {
-        float kv = 0.f;
+        float kv4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          const int row = i * KP + part;
-          if (row < dim) {
-            s[i] *= tok[2 * dim + row];
-            kv = fmaf(s[i], tok[dim + row], kv);
+        for (int i = 0; i < R; i += 4) {
+          if (i < rp) {
+            const float4 g = g4[i / 4], k = k4[i / 4];
+            s[i] *= g.x; s[i + 1] *= g.y; s[i + 2] *= g.z; s[i + 3] *= g.w;
+            kv4[0] = fmaf(s[i], k.x, kv4[0]); kv4[1] = fmaf(s[i + 1], k.y, kv4[1]);
+            kv4[2] = fmaf(s[i + 2], k.z, kv4[2]); kv4[3] = fmaf(s[i + 3], k.w, kv4[3]);
           }
         }
+        float kv = (kv4[0] + kv4[1]) + (kv4[2] + kv4[3]);
 #pragma unroll
         for (int off = COLS_W; off < 32; off <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
-        const float u = sigmoidf_(tok[3 * dim + cols_blk]) * (v - kv);
+        const float u = sigmoidf_(tok[3 * dimp + cols_blk]) * (v - kv);
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          const int row = i * KP + part;
-          if (row < dim) {
-            s[i] = fmaf(tok[dim + row], u, s[i]);
-            o = fmaf(s[i], tok[row], o);
+        for (int i = 0; i < R; i += 4) {
+          if (i < rp) {
+            const float4 k = k4[i / 4], q = q4[i / 4];
+            s[i] = fmaf(k.x, u, s[i]); s[i + 1] = fmaf(k.y, u, s[i + 1]);
+            s[i + 2] = fmaf(k.z, u, s[i + 2]); s[i + 3] = fmaf(k.w, u, s[i + 3]);
+            o4[0] = fmaf(s[i], q.x, o4[0]); o4[1] = fmaf(s[i + 1], q.y, o4[1]);
+            o4[2] = fmaf(s[i + 2], q.z, o4[2]); o4[3] = fmaf(s[i + 3], q.w, o4[3]);
           }
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          const int row = i * KP + part;
-          if (row < dim) {
-            const float kvi = tok[dim + row] * v;
-            o = fmaf(tok[row], fmaf(bonus[i], kvi, s[i]), o);
-            s[i] = fmaf(tok[2 * dim + row], s[i], kvi);
+        for (int i = 0; i < R; i += 4) {
+          if (i < rp) {
+            const float4 g = g4[i / 4], k = k4[i / 4], q = q4[i / 4];
+            const float kv0 = k.x * v, kv1 = k.y * v, kv2 = k.z * v, kv3 = k.w * v;
+            o4[0] = fmaf(q.x, fmaf(bonus[i], kv0, s[i]), o4[0]);
+            o4[1] = fmaf(q.y, fmaf(bonus[i + 1], kv1, s[i + 1]), o4[1]);
+            o4[2] = fmaf(q.z, fmaf(bonus[i + 2], kv2, s[i + 2]), o4[2]);
+            o4[3] = fmaf(q.w, fmaf(bonus[i + 3], kv3, s[i + 3]), o4[3]);
+            s[i] = fmaf(g.x, s[i], kv0); s[i + 1] = fmaf(g.y, s[i + 1], kv1);
+            s[i + 2] = fmaf(g.z, s[i + 2], kv2); s[i + 3] = fmaf(g.w, s[i + 3], kv3);
           }
         }
       }
+      float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
 #pragma unroll
       for (int off = COLS_W; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (col && part == 0)
@@ -272,8 +311,8 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs a, int tc) {
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int row = i * KP + part;
-    if (col && row < dim) S[(size_t)row * vdim + j] = s[i];
+    const int row = row0 + i;
+    if (col && i < rp && row < dim) S[(size_t)row * vdim + j] = s[i];
   }
 }
 
@@ -390,22 +429,29 @@ FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* 
   if (n_seqs == 0) return 0;
   ScanArgs a{q, q_ld, k, k_ld, v, v_ld, g, g_ld, beta, beta_ld, bonus, state, state_stride,
              s_offset, out, cu_tokens, slots, H, rep, dim, vdim};
+  // a column is shared by kp lanes: eight key rows a lane where the head allows it
+  // (a token's step is a chain of dependent instructions; fewer rows a lane shorten it)
   int kp = 1;
-  while (kp * R < dim) kp *= 2;
+  while (kp * 8 < dim && kp < 32) kp *= 2;
   const int cols_w = 32 / kp;
   const int warps_needed = (vdim + cols_w - 1) / cols_w;
-  const int warps = warps_needed < 4 ? warps_needed : 4;
+  const int most = kp >= 16 ? 8 : 4;  // (a wide head's record takes more threads to copy)
+  const int warps = warps_needed < most ? warps_needed : most;
   dim3 grid(n_seqs, H, (warps_needed + warps - 1) / warps);
+  // key rows a lane group holds: consecutive, a multiple of four
+  const int rp = ((dim + kp - 1) / kp + 3) / 4 * 4;
   // tokens staged at a time: two buffers within the 48 KB that need no opt-in
-  const int per_tok = 3 * dim + warps * cols_w + 1;
+  const int per_tok = (3 * kp * rp + warps * cols_w + 1 + 3) / 4 * 4;
   int tc = 16;
   while (tc > 1 && (size_t)2 * tc * per_tok * 4 > 48 * 1024) tc /= 2;
   const size_t smem = (size_t)2 * tc * per_tok * 4;
   FB_REQUIRE(smem <= 48 * 1024, "state_scan: a token's inputs (%d floats) do not fit", per_tok);
+  FB_REQUIRE(per_tok <= 8 * warps * 32, "state_scan: %d inputs a token are more than the block's "
+             "threads copy", per_tok);
 #define FB_SCAN(KP)                                                                              \
   case KP:                                                                                       \
-    if (mode == 0) fb_launch(scan_kernel<0, KP>, grid, dim3(warps * 32), smem, stream, a, tc);   \
-    else fb_launch(scan_kernel<1, KP>, grid, dim3(warps * 32), smem, stream, a, tc);             \
+    if (mode == 0) fb_launch(scan_kernel<0, KP>, grid, dim3(warps * 32), smem, stream, a, tc, rp); \
+    else fb_launch(scan_kernel<1, KP>, grid, dim3(warps * 32), smem, stream, a, tc, rp);      \
     break;
   switch (kp) {
     FB_SCAN(1) FB_SCAN(2) FB_SCAN(4) FB_SCAN(8) FB_SCAN(16) FB_SCAN(32)

@@ -100,14 +100,19 @@ struct SinkMask {
   float scale, steep;
 };
 
-template <typename T>
+// VEC (value size a multiple of 8, 16-byte aligned value rows): a value row is
+// read as 16-byte pieces by `lpr` neighbouring lanes and 32 / lpr keys are worked at
+// a time, every lane's loads of a chunk independent of one another; the lanes that
+// share a piece add their sums up once, at the end. Otherwise a lane owns the
+// elements lane, lane + 32, ... and keys go one by one.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long long out_stride,
                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                       const int* __restrict__ page_table, int max_pages, const T* k_cache,
                       const T* v_cache, long long k_page, long long k_head, long long v_page,
                       long long v_head, SinkMask mask, int H, int G, int D, int VD, int splits,
-                      float* __restrict__ partial) {
+                      float* __restrict__ partial, int lpr) {
   fb_pdl_wait();
   __shared__ float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -175,17 +180,52 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
 #pragma unroll
       for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= corr;
       const int n = min(32, end - j0);
-      for (int jj = 0; jj < n; ++jj) {
-        const float pj = __shfl_sync(0xffffffffu, p, jj);
-        const long long off = __shfl_sync(0xffffffffu, v_off, jj);
-        const T* vrow = vbase + off;
+      if (VEC) {
+        const int d0 = (lane % lpr) * 8, sub = lane / lpr, ks = 32 / lpr;
+        for (int jj = 0; jj < n; jj += ks) {  // uniform trip count; lanes past n add nothing
+          const int key = jj + sub;
+          const float pj = __shfl_sync(0xffffffffu, p, key & 31);
+          const long long off = __shfl_sync(0xffffffffu, v_off, key & 31);
+          if (key < n && d0 < VD) {
+            float vv[8];
+            load8<T>(vbase + off + d0, vv);
 #pragma unroll
-        for (int i = 0; i < MAX_D / 32; ++i) {
-          const int d = lane + 32 * i;
-          if (d < VD) acc[i] = fmaf(pj, fb_load_coherent<T>(vrow + d), acc[i]);
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(pj, vv[e], acc[e]);
+          }
+        }
+      } else {
+        for (int jj = 0; jj < n; ++jj) {
+          const float pj = __shfl_sync(0xffffffffu, p, jj);
+          const long long off = __shfl_sync(0xffffffffu, v_off, jj);
+          const T* vrow = vbase + off;
+#pragma unroll
+          for (int i = 0; i < MAX_D / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < VD) acc[i] = fmaf(pj, fb_load_coherent<T>(vrow + d), acc[i]);
+          }
         }
       }
     }
+  }
+  if (VEC) {
+    // the lanes that hold the same piece of the row (one per key worked at a time)
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      for (int off = lpr; off < 32; off <<= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+    const int d0 = lane * 8;  // after the sum every group of lpr lanes holds the whole row
+    if (splits > 1) {
+      float* dst = partial + (((size_t)t * H + a) * splits + blockIdx.z) * (VD + 2);
+      if (lane == 0) { dst[0] = m; dst[1] = l; }
+      if (lane < lpr && d0 < VD)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dst[2 + d0 + e] = acc[e];
+      return;
+    }
+    const float inv = 1.0f / l;
+    if (lane < lpr && d0 < VD)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[d0 + e] = fb_from_float<T>(acc[e] * inv);
+    return;
   }
   if (splits > 1) {
     float* dst = partial + (((size_t)t * H + a) * splits + blockIdx.z) * (VD + 2);
@@ -283,10 +323,20 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
   if (T == 0) return 0;
   SinkMask mask{window, keep_first, sink ? 1 : 0, scale, steep};
   dim3 grid(T, (H + WARPS - 1) / WARPS, splits);
-  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E>, dim3(grid), dim3(WARPS * 32), 0,
-      stream, (const E*)q, q_stride, (E*)out, out_stride, positions, seq_of_token, page_table,
-      max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head, v_page, v_head, mask, H, G,
-      D, VD, splits, partial)));
+  const bool vec = VD % 8 == 0 && v_page % 8 == 0 && v_head % 8 == 0 && ((uintptr_t)v_cache % 32) == 0;
+  int lpr = 1;
+  while (lpr * 8 < VD) lpr *= 2;  // lanes that share a value row: a power of two, at most 32
+  if (vec) {
+    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E, true>, dim3(grid),
+        dim3(WARPS * 32), 0, stream, (const E*)q, q_stride, (E*)out, out_stride, positions,
+        seq_of_token, page_table, max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head,
+        v_page, v_head, mask, H, G, D, VD, splits, partial, lpr)));
+  } else {
+    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E, false>, dim3(grid),
+        dim3(WARPS * 32), 0, stream, (const E*)q, q_stride, (E*)out, out_stride, positions,
+        seq_of_token, page_table, max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head,
+        v_page, v_head, mask, H, G, D, VD, splits, partial, lpr)));
+  }
   if (splits > 1) {
     int rc = fb_check_launch("attention_sink");
     if (rc) return rc;
