@@ -73,6 +73,102 @@ __global__ void ln_add_ln_kernel(const TY* y, const float* __restrict__ w1,
     o[i] = fb_from_float<TO>((row[i] - mean) * r * w2[i] + b2[i]);
 }
 
+// The same for rows of whole groups of four elements on 16-byte boundaries: every
+// global and shared access is a float4 (or four 16-bit values in one 8-byte piece).
+template <typename TD>
+__device__ __forceinline__ float4 ld4(const TD* p);
+template <>
+__device__ __forceinline__ float4 ld4<float>(const float* p) {
+  return __ldcg(reinterpret_cast<const float4*>(p));
+}
+template <>
+__device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(p));
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename TD>
+__device__ __forceinline__ void st4(TD* p, float4 v);
+template <>
+__device__ __forceinline__ void st4<float>(float* p, float4 v) {
+  *reinterpret_cast<float4*>(p) = v;
+}
+template <>
+__device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename TY, typename TO>
+__global__ void ln_add_ln_vec_kernel(const TY* y, const float* __restrict__ w1,
+                                     const float* __restrict__ b1, float* resid,
+                                     const float* __restrict__ w2, const float* __restrict__ b2,
+                                     TO* __restrict__ out, int W, float eps, float inv_w) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  extern __shared__ __align__(16) float row[];  // W floats
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * W;
+  float* x = resid + base;
+  float4* row4 = reinterpret_cast<float4*>(row);
+  const int n4 = W / 4;
+  if (y != nullptr && w1 == nullptr) {
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 a = ld4<float>(x + 4 * i), d = ld4<TY>(y + base + 4 * i);
+      const float4 v = make_float4(a.x + d.x, a.y + d.y, a.z + d.z, a.w + d.w);
+      st4<float>(x + 4 * i, v);
+      row4[i] = v;
+    }
+  } else if (y != nullptr) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = ld4<TY>(y + base + 4 * i);
+      row4[i] = v;
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    const float mean = fb_block_sum(s, scratch) * inv_w;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = row4[i];
+      const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+      q += (a * a + b * b) + (c * c + d * d);
+    }
+    const float r = 1.0f / sqrtf(fb_block_sum(q, scratch) * inv_w + eps);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = row4[i], g = ld4<float>(w1 + 4 * i), h = ld4<float>(b1 + 4 * i);
+      const float4 a = ld4<float>(x + 4 * i);
+      const float4 o = make_float4(a.x + ((v.x - mean) * r * g.x + h.x), a.y + ((v.y - mean) * r * g.y + h.y),
+                                   a.z + ((v.z - mean) * r * g.z + h.z), a.w + ((v.w - mean) * r * g.w + h.w));
+      st4<float>(x + 4 * i, o);
+      row4[i] = o;
+    }
+  } else if (out != nullptr) {
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) row4[i] = ld4<float>(x + 4 * i);
+  }
+  if (out == nullptr) return;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 v = row4[i];
+    s += (v.x + v.y) + (v.z + v.w);
+  }
+  const float mean = fb_block_sum(s, scratch) * inv_w;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 v = row4[i];
+    const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+    q += (a * a + b * b) + (c * c + d * d);
+  }
+  const float r = 1.0f / sqrtf(fb_block_sum(q, scratch) * inv_w + eps);
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 v = row4[i], g = ld4<float>(w2 + 4 * i), h = ld4<float>(b2 + 4 * i);
+    st4<TO>(out + base + 4 * i, make_float4((v.x - mean) * r * g.x + h.x, (v.y - mean) * r * g.y + h.y,
+                                            (v.z - mean) * r * g.z + h.z, (v.w - mean) * r * g.w + h.w));
+  }
+}
+
 // x[t, :] = table[ids[t], :] * scale + pe(positions[t]), pe[2i] = sin(p f_i),
 // pe[2i+1] = cos(p f_i). The angle is the double-precision product of the
 // position and a double-precision frequency, so that it is exact to 32 bits
@@ -132,16 +228,29 @@ FB_API int fb_ln_add_ln(const void* y, int y_dtype, const float* w1, const float
   FB_REQUIRE(out == nullptr || (w2 && b2), "ln_add_ln: the norm of the sum has no weight or bias");
   FB_REQUIRE((size_t)W * 4 <= 200 * 1024, "ln_add_ln: rows of %d do not fit shared memory", W);
   if (T == 0 || (y == nullptr && out == nullptr)) return 0;
-  const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
   const size_t smem = (size_t)W * 4;
+  const bool vec = W % 4 == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)resid % 16) == 0 &&
+                   ((uintptr_t)out % 16) == 0 && ((uintptr_t)w1 % 16) == 0 &&
+                   ((uintptr_t)b1 % 16) == 0 && ((uintptr_t)w2 % 16) == 0 && ((uintptr_t)b2 % 16) == 0;
+  // (the block width decides the order of a row's sums, so it depends on W alone)
+  const int threads = vec ? (W >= 4096 ? 512 : (W >= 1024 ? 256 : 128))
+                          : (W >= 2048 ? 512 : (W >= 512 ? 256 : 128));
 #define FB_LN_LAUNCH(TY, TO)                                                                   \
   do {                                                                                         \
     static bool seen[64];                                                                      \
     if (smem > 48 * 1024 && fb_first_use_on_device(seen))                                      \
       cudaFuncSetAttribute(ln_add_ln_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            200 * 1024);                                                        \
-    fb_launch(ln_add_ln_kernel<TY, TO>, dim3(T), dim3(threads), smem, stream, (const TY*)y, w1, \
-              b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W);                           \
+    static bool seen_vec[64];                                                                  \
+    if (smem > 48 * 1024 && fb_first_use_on_device(seen_vec))                                  \
+      cudaFuncSetAttribute(ln_add_ln_vec_kernel<TY, TO>,                                       \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
+    if (vec)                                                                                   \
+      fb_launch(ln_add_ln_vec_kernel<TY, TO>, dim3(T), dim3(threads), smem, stream,            \
+                (const TY*)y, w1, b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W);       \
+    else                                                                                       \
+      fb_launch(ln_add_ln_kernel<TY, TO>, dim3(T), dim3(threads), smem, stream, (const TY*)y,  \
+                w1, b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W);                     \
   } while (0)
   const int yd = y ? y_dtype : FB_F32, od = out ? out_dtype : FB_F32;
   FB_DISPATCH_DTYPE(yd, TY, FB_DISPATCH_DTYPE(od, TO, FB_LN_LAUNCH(TY, TO)));
