@@ -181,7 +181,6 @@ FB_API int fb_moe_experts_rows(const void* h, int dtype, const void* gate_up, co
 //   fb_moe_combine    out[t] = sum_c weight[t, c] * y_sorted[place[t, c]] in the
 //                     order of c, so the sum does not depend on the sorting
 namespace {
-constexpr int CHUNK = 8;  // input rows an expert's block holds at a time
 
 __global__ void moe_sort_kernel(const int* chosen, int n_pairs, int E, int* __restrict__ counts,
                                 int* __restrict__ starts, int* __restrict__ place,
@@ -282,12 +281,15 @@ __device__ __forceinline__ void w8<__nv_bfloat16>(const __nv_bfloat16* __restric
 // A block owns (expert e, weight rows [row0, row0 + rows)); K % 8 == 0 and the
 // weight rows 16-byte aligned (checked by the launcher). NR weight rows are
 // walked together by a warp: GATED walks a gate row and its up row (NR = 2).
-// xs: the chunk's input rows [CHUNK][K] as floats in shared memory.
-template <typename T, typename TX, bool GATED>
+// xs: the chunk's input rows [CHUNK][K] as floats in shared memory. (A form with two
+// rows a chunk for single-token steps, four blocks a SM, was slower: 141 against
+// 103 us a call at 16 pairs over 16 experts of 2048 x 2048.)
+// `pair_at` given: the sorted row `at` is row pair_at[at] / top of x (no gathered copy).
+template <typename T, typename TX, bool GATED, int CHUNK>
 __global__ void __launch_bounds__(256, 3)
 moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const int* starts,
                    float* __restrict__ out, long long ldo, int K, int N, int rows_per_block,
-                   float limit, float alpha) {
+                   float limit, float alpha, const int* pair_at, int top) {
   fb_pdl_wait();
   extern __shared__ float xs[];  // [CHUNK][K]
   const int e = blockIdx.x;
@@ -303,7 +305,8 @@ moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const in
     __syncthreads();
     for (int i = threadIdx.x; i < nc * K; i += blockDim.x) {
       const int r = i / K, k = i - r * K;
-      xs[r * K + k] = fb_load_coherent<TX>(x + (size_t)(c0 + r) * ldx + k);
+      const size_t src = pair_at != nullptr ? (size_t)(pair_at[c0 + r] / top) : (size_t)(c0 + r);
+      xs[r * K + k] = fb_load_coherent<TX>(x + src * ldx + k);
     }
     __syncthreads();
     for (int row = row0 + warp; row < row1; row += nwarps) {
@@ -406,26 +409,34 @@ FB_API int fb_moe_glu(const void* gu, int in_dtype, void* out, int out_dtype, in
 // gated = 0: x rows are float32 (the activations), w = down [E, N, K], out = products
 FB_API int fb_moe_grouped(int gated, const void* x, long long ldx, const void* w, int w_dtype,
                           const int* starts, float* out, long long ldo, int E, int K, int N,
-                          float limit, float alpha, int sm_count, cudaStream_t stream) {
+                          float limit, float alpha, int sm_count, const int* pair_at, int top,
+                          int n_pairs, cudaStream_t stream) {
   FB_REQUIRE(E > 0 && K > 0 && N > 0 && ldx >= K && ldo >= N, "moe_grouped: bad sizes");
   FB_REQUIRE(K % 8 == 0 && ((uintptr_t)w % 16) == 0 && ldx % 4 == 0,
              "moe_grouped: K = %d must be a multiple of 8 and the matrices 16-byte aligned", K);
-  const size_t smem = (size_t)CHUNK * K * 4;
+  const int chunk = 8;
+  const size_t smem = (size_t)chunk * K * 4;
   FB_REQUIRE(smem <= 200 * 1024, "moe_grouped: %d input rows of %d do not fit shared memory",
-             CHUNK, K);
+             chunk, K);
+  FB_REQUIRE(pair_at == nullptr || top > 0, "moe_grouped: rows by pair need the pairs a token");
   // row slices so that the experts in use cover the SMs a few times over
   int slices = (6 * (sm_count > 0 ? sm_count : 148) + E - 1) / E;
   int rows = (N + slices - 1) / slices;
   rows = (rows + 7) / 8 * 8;
   dim3 grid(E, (N + rows - 1) / rows);
-#define FB_MOE_GROUPED(T_, TX_, G_)                                                             \
+#define FB_MOE_GROUPED_C(T_, TX_, G_, C_)                                                       \
   do {                                                                                          \
     static bool seen[64];                                                                       \
-    if (smem > 48 * 1024 && fb_first_use_on_device(seen))                                       \
-      cudaFuncSetAttribute(moe_grouped_kernel<T_, TX_, G_>,                                     \
+    if (fb_first_use_on_device(seen))                                                           \
+      cudaFuncSetAttribute(moe_grouped_kernel<T_, TX_, G_, C_>,                                 \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);            \
-    fb_launch(moe_grouped_kernel<T_, TX_, G_>, grid, dim3(256), smem, stream, (const TX_*)x,    \
-              ldx, (const T_*)w, starts, out, ldo, K, N, rows, limit, alpha);                   \
+    fb_launch(moe_grouped_kernel<T_, TX_, G_, C_>, grid, dim3(256), smem, stream,               \
+              (const TX_*)x, ldx, (const T_*)w, starts, out, ldo, K, N, rows, limit, alpha,     \
+              pair_at, top);                                                                    \
+  } while (0)
+#define FB_MOE_GROUPED(T_, TX_, G_)                                                             \
+  do {                                                                                          \
+    FB_MOE_GROUPED_C(T_, TX_, G_, 8);                                                           \
   } while (0)
   if (gated) {
     FB_DISPATCH_DTYPE(w_dtype, T_, FB_MOE_GROUPED(T_, T_, true));
@@ -433,6 +444,7 @@ FB_API int fb_moe_grouped(int gated, const void* x, long long ldx, const void* w
     FB_DISPATCH_DTYPE(w_dtype, T_, FB_MOE_GROUPED(T_, float, false));
   }
 #undef FB_MOE_GROUPED
+#undef FB_MOE_GROUPED_C
   return fb_check_launch("moe_grouped");
 }
 

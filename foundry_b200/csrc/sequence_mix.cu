@@ -174,8 +174,11 @@ __device__ __forceinline__ void cp_async_wait_but_one() {
 // Per token: q [dimp] | k [dimp] | g [dimp] | v [the block's columns] | beta | padding,
 // dimp = KP * rp the key rows padded so that lane group `part` holds the rp
 // consecutive rows part * rp .. (a multiple of 4: they are read as float4).
-template <int MODE, int KP>
-__global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc, int rp) {
+// RP: key rows a lane holds (4 or 8, or 16 for heads of more than 256 key channels);
+// MINE: elements of a token's record a thread copies at most.
+template <int MODE, int KP, int RP, int MINE>
+__global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
+  constexpr int rp = RP;
   fb_pdl_wait();
   constexpr int COLS_W = 32 / KP;  // columns a warp holds
   extern __shared__ __align__(16) float sbuf[];
@@ -196,11 +199,15 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc, int rp) {
   const long long qoff = (long long)(h / a.rep) * dim, goff = (long long)h * dim;
   const int per_tok = (3 * dimp + cols_blk + 1 + 3) / 4 * 4;
   const int row0 = part * rp;  // this thread's first key row
+  // A token's output is a sum over the KP lanes of a column. It is not needed for the
+  // next token, so the lanes' shares wait in shared memory and are added up once per
+  // chunk of tokens (every lane group takes its share of the chunk's tokens), instead
+  // of a chain of shuffles inside every token's step.
+  float* opart = sbuf + (size_t)2 * tc * per_tok + (size_t)warp * 32 * tc;  // [tc][32] a warp
 
   // what a thread copies is the same for every token: its elements of a token's record
   // are found once (at most four a thread), then only the token's row offset changes
-  constexpr int MINE = 8;
-  const float* src0[MINE];
+  const float* src0[MINE];  // where the thread's element e of the NEXT token to copy lies
   long long ld[MINE];
   int at[MINE];
 #pragma unroll
@@ -223,34 +230,40 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc, int rp) {
       src = a.beta + h;
       step = a.beta_ld;
     }
-    src0[e] = src; ld[e] = step; at[e] = c < per_tok ? c : -1;
+    src0[e] = src == nullptr ? nullptr : src + (size_t)start * step;
+    ld[e] = step; at[e] = c < per_tok ? c : -1;
   }
-  auto stage = [&](int buf, int t0, int nt) {
+  // (tokens are staged in order, so the source pointers only ever move on by one row)
+  auto stage = [&](int buf, int nt) {
     float* dst = sbuf + (size_t)buf * tc * per_tok;
-    for (int r = 0; r < nt; ++r) {
+    for (int r = 0; r < nt; ++r, dst += per_tok) {
 #pragma unroll
       for (int e = 0; e < MINE; ++e) {
         if (at[e] >= 0) {
-          if (src0[e] != nullptr) cp_async4(dst + r * per_tok + at[e], src0[e] + (size_t)(t0 + r) * ld[e]);
-          else dst[r * per_tok + at[e]] = 0.f;
+          if (src0[e] != nullptr) {
+            cp_async4(dst + at[e], src0[e]);
+            src0[e] += ld[e];
+          } else {
+            dst[at[e]] = 0.f;
+          }
         }
       }
     }
   };
 
-  float s[R], bonus[R];
+  float s[RP], bonus[RP];
 #pragma unroll
-  for (int i = 0; i < R; ++i) {
+  for (int i = 0; i < RP; ++i) {
     const int row = row0 + i;
-    const bool ok = i < rp && row < dim;
+    const bool ok = row < dim;
     s[i] = (col && ok) ? S[(size_t)row * vdim + j] : 0.f;
     bonus[i] = (MODE == 1 && ok) ? a.bonus[goff + row] : 0.f;
   }
-  stage(0, start, min(tc, n));
+  stage(0, min(tc, n));
   cp_async_commit();
   for (int c0 = 0; c0 < n; c0 += tc) {
     const int buf = (c0 / tc) & 1, nt = min(tc, n - c0);
-    if (c0 + tc < n) stage(buf ^ 1, start + c0 + tc, min(tc, n - c0 - tc));
+    if (c0 + tc < n) stage(buf ^ 1, min(tc, n - c0 - tc));
     cp_async_commit();  // (an empty group when nothing follows: the count below stays right)
     cp_async_wait_but_one();
     __syncthreads();
@@ -264,8 +277,8 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc, int rp) {
       if (MODE == 0) {
         float kv4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < R; i += 4) {
-          if (i < rp) {
+        for (int i = 0; i < RP; i += 4) {
+          {
             const float4 g = g4[i / 4], k = k4[i / 4];
             s[i] *= g.x; s[i + 1] *= g.y; s[i + 2] *= g.z; s[i + 3] *= g.w;
             kv4[0] = fmaf(s[i], k.x, kv4[0]); kv4[1] = fmaf(s[i + 1], k.y, kv4[1]);
@@ -277,8 +290,8 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc, int rp) {
         for (int off = COLS_W; off < 32; off <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
         const float u = sigmoidf_(tok[3 * dimp + cols_blk]) * (v - kv);
 #pragma unroll
-        for (int i = 0; i < R; i += 4) {
-          if (i < rp) {
+        for (int i = 0; i < RP; i += 4) {
+          {
             const float4 k = k4[i / 4], q = q4[i / 4];
             s[i] = fmaf(k.x, u, s[i]); s[i + 1] = fmaf(k.y, u, s[i + 1]);
             s[i + 2] = fmaf(k.z, u, s[i + 2]); s[i + 3] = fmaf(k.w, u, s[i + 3]);
@@ -288,8 +301,8 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc, int rp) {
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < R; i += 4) {
-          if (i < rp) {
+        for (int i = 0; i < RP; i += 4) {
+          {
             const float4 g = g4[i / 4], k = k4[i / 4], q = q4[i / 4];
             const float kv0 = k.x * v, kv1 = k.y * v, kv2 = k.z * v, kv3 = k.w * v;
             o4[0] = fmaf(q.x, fmaf(bonus[i], kv0, s[i]), o4[0]);
@@ -301,18 +314,21 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc, int rp) {
           }
         }
       }
-      float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-#pragma unroll
-      for (int off = COLS_W; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (col && part == 0)
-        a.out[(size_t)(start + c0 + r) * a.H * vdim + (size_t)h * vdim + j] = o;
+      opart[r * 32 + lane] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     }
-    __syncthreads();  // the buffer is refilled by the next iteration's copies
+    __syncwarp();
+    for (int r = part; r < nt; r += KP) {
+      float o = 0.f;
+#pragma unroll
+      for (int p = 0; p < KP; ++p) o += opart[r * 32 + p * COLS_W + (lane % COLS_W)];
+      if (col) a.out[(size_t)(start + c0 + r) * a.H * vdim + (size_t)h * vdim + j] = o;
+    }
+    __syncthreads();  // the buffers are refilled by the next iteration
   }
 #pragma unroll
-  for (int i = 0; i < R; ++i) {
+  for (int i = 0; i < RP; ++i) {
     const int row = row0 + i;
-    if (col && i < rp && row < dim) S[(size_t)row * vdim + j] = s[i];
+    if (col && row < dim) S[(size_t)row * vdim + j] = s[i];
   }
 }
 
@@ -433,31 +449,57 @@ FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* 
   // (a token's step is a chain of dependent instructions; fewer rows a lane shorten it)
   int kp = 1;
   while (kp * 8 < dim && kp < 32) kp *= 2;
+  // few blocks (a prompt of one or two sequences): four rows a lane make twice the
+  // warps with half the work each, which is what fills an SM's schedulers then
+  {
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess)
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int cols_blk8 = 4 * (32 / kp);
+    const long long blocks = (long long)n_seqs * H * ((vdim + cols_blk8 - 1) / cols_blk8);
+    if (blocks < 2LL * sms && kp < 32 && (dim + 2 * kp - 1) / (2 * kp) <= 4) kp *= 2;
+  }
   const int cols_w = 32 / kp;
   const int warps_needed = (vdim + cols_w - 1) / cols_w;
   const int most = kp >= 16 ? 8 : 4;  // (a wide head's record takes more threads to copy)
   const int warps = warps_needed < most ? warps_needed : most;
   dim3 grid(n_seqs, H, (warps_needed + warps - 1) / warps);
-  // key rows a lane group holds: consecutive, a multiple of four
-  const int rp = ((dim + kp - 1) / kp + 3) / 4 * 4;
+  // key rows a lane holds: 4 or 8, or 16 for heads of more than 256 key channels
+  const int rows = (dim + kp - 1) / kp;
+  const int rp = rows <= 4 ? 4 : rows <= 8 ? 8 : 16;
   // tokens staged at a time: two buffers within the 48 KB that need no opt-in
   const int per_tok = (3 * kp * rp + warps * cols_w + 1 + 3) / 4 * 4;
   int tc = 16;
   while (tc > 1 && (size_t)2 * tc * per_tok * 4 > 48 * 1024) tc /= 2;
-  const size_t smem = (size_t)2 * tc * per_tok * 4;
+  while (tc > 1 && (size_t)(2 * tc * per_tok + warps * 32 * tc) * 4 > 48 * 1024) tc /= 2;
+  const size_t smem = (size_t)(2 * tc * per_tok + warps * 32 * tc) * 4;
   FB_REQUIRE(smem <= 48 * 1024, "state_scan: a token's inputs (%d floats) do not fit", per_tok);
-  FB_REQUIRE(per_tok <= 8 * warps * 32, "state_scan: %d inputs a token are more than the block's "
-             "threads copy", per_tok);
-#define FB_SCAN(KP)                                                                              \
-  case KP:                                                                                       \
-    if (mode == 0) fb_launch(scan_kernel<0, KP>, grid, dim3(warps * 32), smem, stream, a, tc, rp); \
-    else fb_launch(scan_kernel<1, KP>, grid, dim3(warps * 32), smem, stream, a, tc, rp);      \
+  const int mine = (per_tok + warps * 32 - 1) / (warps * 32);
+  FB_REQUIRE(mine <= 8, "state_scan: %d inputs a token are more than the block's threads copy",
+             per_tok);
+#define FB_SCAN_LAUNCH(M_, KP_, RP_, MINE_) \
+  fb_launch(scan_kernel<M_, KP_, RP_, MINE_>, grid, dim3(warps * 32), smem, stream, a, tc)
+#define FB_SCAN_MINE(M_, KP_, RP_)                       \
+  do {                                                   \
+    if (mine <= 2) FB_SCAN_LAUNCH(M_, KP_, RP_, 2);      \
+    else FB_SCAN_LAUNCH(M_, KP_, RP_, 8);                \
+  } while (0)
+#define FB_SCAN(KP_)                                                \
+  case KP_:                                                         \
+    if (rp == 4) { if (mode == 0) FB_SCAN_MINE(0, KP_, 4); else FB_SCAN_MINE(1, KP_, 4); } \
+    else { if (mode == 0) FB_SCAN_MINE(0, KP_, 8); else FB_SCAN_MINE(1, KP_, 8); }         \
     break;
-  switch (kp) {
-    FB_SCAN(1) FB_SCAN(2) FB_SCAN(4) FB_SCAN(8) FB_SCAN(16) FB_SCAN(32)
-    default: return fb_fail(1, "state_scan: no kernel for %d lanes a column", kp);
+  if (kp == 32 && rp == 16) {
+    if (mode == 0) FB_SCAN_MINE(0, 32, 16); else FB_SCAN_MINE(1, 32, 16);
+  } else {
+    switch (kp) {
+      FB_SCAN(1) FB_SCAN(2) FB_SCAN(4) FB_SCAN(8) FB_SCAN(16) FB_SCAN(32)
+      default: return fb_fail(1, "state_scan: no kernel for %d lanes a column", kp);
+    }
   }
 #undef FB_SCAN
+#undef FB_SCAN_MINE
+#undef FB_SCAN_LAUNCH
   return fb_check_launch("state_scan");
 }
 

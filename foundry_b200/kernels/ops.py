@@ -123,7 +123,7 @@ _SIGNATURES = {
     "fb_moe_glu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p,
                    c_int, c_void_p],
     "fb_moe_grouped": [c_int, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_int,
-                       c_int, c_int, c_float, c_float, c_int, c_void_p],
+                       c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_int, c_void_p],
     "fb_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -1838,10 +1838,11 @@ def moe_grouped_fits(K: int) -> bool:
 
 
 def moe_grouped(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: bool,
-                limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+                limit: float = 0.0, alpha: float = 0.0, by_token: bool = False) -> torch.Tensor:
     """For every expert, its sorted rows of `x` times its matrix in `w` ([E, N, K],
     or [E, 2N, K] gate rows then up rows when `gated`, which also applies the
-    activation); float32 out [pairs, N]."""
+    activation); float32 out [pairs, N]. `by_token`: `x` holds the tokens' rows
+    [T, K] and a pair's row is found through the order (no gathered copy)."""
     E, rows, K = w.shape
     N = rows // 2 if gated else rows
     out = torch.empty((order.pairs, N), dtype=torch.float32, device=x.device)
@@ -1850,7 +1851,8 @@ def moe_grouped(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: boo
     want = w.dtype if gated else torch.float32
     _call("fb_moe_grouped", 1 if gated else 0, _dev(x, "x", want), x.stride(0), _dev(w, "w"),
           code_of(w.dtype), order.starts.data_ptr(), out.data_ptr(), N, E, K, N, float(limit),
-          float(alpha), sm_count(), _stream())
+          float(alpha), sm_count(), order.pair_at.data_ptr() if by_token else 0, order.top,
+          order.pairs, _stream())
     return out
 
 

@@ -70,11 +70,11 @@ class RoutedExperts(Part):
             return ops.moe_experts_rows(x, self.gate_up, self.down, chosen, weights, out,
                                         self.limit, self.alpha)
         order = ops.ExpertOrder(chosen, self.experts)
-        rows = ops.moe_gather(x, order)
         if T >= self.LIBRARY_ROWS and getattr(ctx, "cu_tokens_host", None) is not None:
-            y = self._per_expert_products(rows, order)
+            y = self._per_expert_products(ops.moe_gather(x, order), order)
         else:
-            act = ops.moe_grouped(rows, self.gate_up, order, True, self.limit, self.alpha)
+            act = ops.moe_grouped(x, self.gate_up, order, True, self.limit, self.alpha,
+                                  by_token=True)
             y = ops.moe_grouped(act, self.down, order, False)
         return ops.moe_combine(y, order, weights, out)
 
