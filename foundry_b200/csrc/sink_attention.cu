@@ -112,7 +112,7 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
                       const int* __restrict__ page_table, int max_pages, const T* k_cache,
                       const T* v_cache, long long k_page, long long k_head, long long v_page,
                       long long v_head, SinkMask mask, int H, int G, int D, int VD, int splits,
-                      float* __restrict__ partial, int lpr) {
+                      float* __restrict__ partial, int lpr, int kvec) {
   fb_pdl_wait();
   __shared__ float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -164,11 +164,15 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
         v_off = page * v_page + (long long)r * VD;
         const T* krow = kbase + k_off;
         float dot = 0.f;
-        for (int d = 0; d < D; d += 8) {
-          float kv[8];
-          load8<T>(krow + d, kv);
+        if (kvec) {  // key rows of whole 16-byte pieces
+          for (int d = 0; d < D; d += 8) {
+            float kv[8];
+            load8<T>(krow + d, kv);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(qs[warp][d + e], kv[e], dot);
+            for (int e = 0; e < 8; ++e) dot = fmaf(qs[warp][d + e], kv[e], dot);
+          }
+        } else {
+          for (int d = 0; d < D; ++d) dot = fmaf(qs[warp][d], fb_load_coherent<T>(krow + d), dot);
         }
         s = dot * mask.scale - slope * (float)(pos - j);
       }
@@ -313,10 +317,9 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
   FB_REQUIRE(T >= 0 && H > 0 && G > 0 && D > 0 && VD > 0, "attention_sink: bad sizes");
   FB_REQUIRE(H % G == 0, "attention_sink: %d query heads are not a multiple of %d key-value heads",
              H, G);
-  FB_REQUIRE(D % 8 == 0 && D <= MAX_D && VD <= MAX_D,
-             "attention_sink: key size %d must be a multiple of 8, and both sizes at most %d "
-             "(value size %d)", D, MAX_D, VD);
-  FB_REQUIRE(k_page % 8 == 0 && k_head % 8 == 0, "attention_sink: key rows are not 16-byte aligned");
+  FB_REQUIRE(D <= MAX_D && VD <= MAX_D, "attention_sink: key size %d and value size %d must be "
+             "at most %d", D, VD, MAX_D);
+  const int kvec = D % 8 == 0 && k_page % 8 == 0 && k_head % 8 == 0 && ((uintptr_t)k_cache % 32) == 0;
   FB_REQUIRE(window >= 0 && keep_first >= 0 && max_pages > 0, "attention_sink: bad mask");
   FB_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || partial != nullptr),
              "attention_sink: %d runs need a workspace", splits);
@@ -330,12 +333,12 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
     FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E, true>, dim3(grid),
         dim3(WARPS * 32), 0, stream, (const E*)q, q_stride, (E*)out, out_stride, positions,
         seq_of_token, page_table, max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head,
-        v_page, v_head, mask, H, G, D, VD, splits, partial, lpr)));
+        v_page, v_head, mask, H, G, D, VD, splits, partial, lpr, kvec)));
   } else {
     FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E, false>, dim3(grid),
         dim3(WARPS * 32), 0, stream, (const E*)q, q_stride, (E*)out, out_stride, positions,
         seq_of_token, page_table, max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head,
-        v_page, v_head, mask, H, G, D, VD, splits, partial, lpr)));
+        v_page, v_head, mask, H, G, D, VD, splits, partial, lpr, kvec)));
   }
   if (splits > 1) {
     int rc = fb_check_launch("attention_sink");

@@ -84,6 +84,10 @@ def build_rupotar_spec(config: RupotarConfig) -> ModelSpec:
         architecture=ARCHITECTURE, hidden_size=config.width, vocab_size=config.vocab,
         max_positions=MAX_POSITIONS, layers=tuple(layers), schedule=schedule, final_norm=norm,
         embedding_name="embed", final_norm_prefix="final.norm", output_head_name="head",
+        # a layer without a feed-forward has no use for the norms around one; a file
+        # that carries them all the same is still this model
+        ignorable_tensors=tuple(f"l{i}.norm2{tail}" for i, layer in enumerate(config.layers)
+                                if layer.mlp is None for tail in ("", ".b", "b", "b.b")),
         embedding=PartSpec("scaled_sinusoidal", {"width": config.width,
                                                  "scale": config.embedding_scale,
                                                  "base": POSITION_BASE}),

@@ -42,9 +42,8 @@ class SinkWindowAttention(Part):
                  dtype: torch.dtype, device: torch.device):
         if kv_heads <= 0 or heads % kv_heads:
             raise ValueError(f"{heads} heads are not a multiple of {kv_heads} key-value heads")
-        if dim % 8 or not 8 <= dim <= 256 or not 1 <= vdim <= 256:
-            raise ValueError(f"key size {dim} must be a multiple of 8 up to 256, value size "
-                             f"{vdim} at most 256")
+        if not 1 <= dim <= 256 or not 1 <= vdim <= 256:
+            raise ValueError(f"key size {dim} and value size {vdim} must be at most 256")
         self.width, self.heads, self.kv_heads, self.dim, self.vdim = width, heads, kv_heads, dim, vdim
         self.scale, self.eps = float(scale), float(eps)
         self.window, self.keep_first = (int(window) if window else 0), int(keep_first or 0)

@@ -154,6 +154,36 @@ def test_feed_forwards_norm_embedding_and_junction_alone(name, dtype):
         assert rel_error(resid.cpu(), want) < bound(dtype, 0.3)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_with_sizes_that_fit_no_vector(dtype):
+    """Key size 12 and value size 20 (no multiple of 8), three heads on one key/value
+    head, no window, no kept tokens: the scalar paths of the CUDA-core kernel."""
+    from foundry_b200.cache import SequenceCache
+    from foundry_b200.config.spec import PartSpec
+    from foundry_b200.parts import MIXERS
+    W, H, d, e = 40, 3, 12, 20
+    m = {"heads": H, "kv_heads": 1, "dim": d, "vdim": e, "scale": 0.4}
+    gen = torch.Generator().manual_seed(9)
+    shapes = {"a.q": (H * d, W), "a.k": (d, W), "a.v": (e, W), "a.o": (W, H * e),
+              "a.q.norm": (H * d,), "a.k.norm": (d,)}
+    weights = {k: (torch.randn(s, generator=gen) * (0.3 if len(s) == 2 else 0.2)
+                   + (0.0 if len(s) == 2 else 1.0)).to(torch.bfloat16).float()
+               for k, s in shapes.items()}
+    part = MIXERS.build(PartSpec("sink_window_attention", {
+        "width": W, "heads": H, "kv_heads": 1, "dim": d, "vdim": e, "scale": 0.4, "eps": 1e-5,
+        "window": None, "keep_first": 0, "steep": 8.0, "sink": True}), dtype=dtype, device=DEV)
+    part.load("a", lambda n: weights[n].to(DEV).to(dtype if weights[n].dim() > 1 else torch.float32))
+    cache = SequenceCache({0: part.cache_request()}, 512, 2, dtype, DEV)
+    x = torch.randn(90, W, generator=gen).to(dtype)
+    want = plain.sink_attention(m, double(weights), "a", x.double(), 1e-5)
+    slot = cache.open_sequence()
+    head = part.forward(make_ctx(cache, [slot], [88]), x[:88].to(DEV), cache.view(0, True))
+    tail = [part.forward(make_ctx(cache, [slot], [1]), x[t:t + 1].to(DEV), cache.view(0, True))
+            for t in (88, 89)]
+    got = torch.cat([head] + tail)
+    assert rel_error(got.float().cpu(), want) < bound(dtype)
+
+
 # ------------------------------------------------------- the window's edges
 def edge_case_inputs(query_at, marker_at, width=8):
     """Rows whose normalised query at `query_at` matches only the key at
