@@ -41,7 +41,9 @@ def _ids(text: str) -> List[int]:
 def _add_model_options(sub, with_context: str) -> None:
     sub.add_argument("--model", help="Folder with config.json and model.safetensors.")
     sub.add_argument("--config", help="A named configuration instead of a folder "
-                                      "(llama-3.2-1b, llama-3.2-3b, llama-3.1-8b, tiny-a, tiny-b); "
+                                      "(llama-3.2-1b, llama-3.2-3b, llama-3.1-8b, tiny-a, tiny-b, "
+                                      "rupotar-1b-layers, rupotar-3b-layers, llama-1b-layers, "
+                                      "llama-3b-layers); "
                                       "needs --random-weights.")
     sub.add_argument("--random-weights", type=int, metavar="SEED", default=None,
                      help="Draw the weights of --config from this seed on the device.")
@@ -151,7 +153,8 @@ def _vocab_size(args) -> int:
         from .config import load_model_config
         return load_model_config(args.model)[1].vocab_size
     from .bench.presets import preset
-    return int(preset(args.config)["vocab_size"])
+    doc = preset(args.config)
+    return int(doc["vocab_size"] if "vocab_size" in doc else doc["vocab"])
 
 
 def check_token_ids(prompts, vocab_size: int) -> None:

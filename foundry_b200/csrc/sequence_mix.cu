@@ -31,11 +31,12 @@ __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log
 // out[m, t, :] = h[t] + (h[t-1] - h[t]) * mu[m], h[t-1] being the state's row
 // for the first token that a sequence brings in this step.
 template <typename T>
-__global__ void token_shift_mix_kernel(const T* h, const float* state, long long state_stride,
+__global__ void token_shift_mix_kernel(const T* h, float* state, long long state_stride,
                                        long long prev_offset, const float* __restrict__ mu,
                                        T* __restrict__ out, const int* __restrict__ seq_of_token,
                                        const int* __restrict__ cu_tokens,
-                                       const int* __restrict__ slots, int T_, int W, int n_mix) {
+                                       const int* __restrict__ slots, int T_, int W, int n_mix,
+                                       int single) {
   fb_pdl_launch();
   fb_pdl_wait();
   const int t = blockIdx.x;
@@ -47,13 +48,16 @@ __global__ void token_shift_mix_kernel(const T* h, const float* state, long long
     return;
   }
   const bool first = t == cu_tokens[seq];
-  const float* prev_state = state + (long long)slots[seq] * state_stride + prev_offset;
+  float* prev_state = state + (long long)slots[seq] * state_stride + prev_offset;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     const float x = fb_load_coherent<T>(h + (size_t)t * W + i);
     const float p = first ? __ldcg(prev_state + i) : fb_load_coherent<T>(h + (size_t)(t - 1) * W + i);
     const float d = p - x;
     for (int m = 0; m < n_mix; ++m)
       out[((size_t)m * T_ + t) * W + i] = fb_from_float<T>(x + d * mu[(size_t)m * W + i]);
+    // `single`: every sequence of the step brings one token, so this block is the only
+    // reader of the sequence's row and may leave the token's input there itself
+    if (single) prev_state[i] = x;
   }
 }
 
@@ -86,12 +90,12 @@ __global__ void state_tail_update_kernel(const T* x, long long ld, float* state,
 // Then the first `n_unit` heads of `dim` channels are scaled to unit length,
 // x / sqrt(sum(x^2) + unit_eps), the first `n_scaled` of them also by `extra`.
 __global__ void conv_silu_unit_kernel(const float* x, long long ld, const float* __restrict__ w,
-                                      int taps, const float* state, long long state_stride,
+                                      int taps, float* state, long long state_stride,
                                       long long tail_offset, float* __restrict__ out, int C,
                                       const int* __restrict__ seq_of_token,
                                       const int* __restrict__ cu_tokens,
                                       const int* __restrict__ slots, int n_unit, int dim,
-                                      int n_scaled, float extra, float unit_eps) {
+                                      int n_scaled, float extra, float unit_eps, int single) {
   fb_pdl_launch();
   fb_pdl_wait();
   extern __shared__ float y[];  // C floats
@@ -103,7 +107,7 @@ __global__ void conv_silu_unit_kernel(const float* x, long long ld, const float*
   }
   const int start = cu_tokens[seq];
   const int n_tail = taps - 1;
-  const float* tail = state + (long long)slots[seq] * state_stride + tail_offset;
+  float* tail = state + (long long)slots[seq] * state_stride + tail_offset;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float acc = 0.f;
     for (int a = 0; a < taps; ++a) {
@@ -111,6 +115,9 @@ __global__ void conv_silu_unit_kernel(const float* x, long long ld, const float*
       const float v = idx >= 0 ? __ldcg(x + (size_t)(start + idx) * ld + c)
                                : __ldcg(tail + (size_t)(n_tail + idx) * C + c);
       acc = fmaf(w[(size_t)c * taps + a], v, acc);
+      // `single` (one token a sequence: this block alone reads the row): the tail moves
+      // on by one input as it is read, a thread touching only its own channel
+      if (single && a > 0) tail[(size_t)(a - 1) * C + c] = v;
     }
     y[c] = acc * sigmoidf_(acc);
   }
@@ -374,15 +381,15 @@ __global__ void unary_cast_kernel(const float* in, long long ld, T* __restrict__
 }
 }  // namespace
 
-FB_API int fb_token_shift_mix(const void* h, int dtype, const float* state, long long state_stride,
+FB_API int fb_token_shift_mix(const void* h, int dtype, float* state, long long state_stride,
                               long long prev_offset, const float* mu, void* out,
                               const int* seq_of_token, const int* cu_tokens, const int* slots,
-                              int T, int W, int n_mix, cudaStream_t stream) {
+                              int T, int W, int n_mix, int single, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && W > 0 && n_mix > 0, "token_shift_mix: bad sizes");
   if (T == 0) return 0;
   FB_DISPATCH_DTYPE(dtype, E, (fb_launch(token_shift_mix_kernel<E>, dim3(T), dim3(256), 0, stream,
       (const E*)h, state, state_stride, prev_offset, mu, (E*)out, seq_of_token, cu_tokens, slots,
-      T, W, n_mix)));
+      T, W, n_mix, single)));
   return fb_check_launch("token_shift_mix");
 }
 
@@ -399,10 +406,10 @@ FB_API int fb_state_tail_update(const void* x, int dtype, long long ld, float* s
 }
 
 FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, int taps,
-                             const float* state, long long state_stride, long long tail_offset,
+                             float* state, long long state_stride, long long tail_offset,
                              float* out, int C, const int* seq_of_token, const int* cu_tokens,
                              const int* slots, int n_unit, int dim, int n_scaled, float extra,
-                             float unit_eps, int T, cudaStream_t stream) {
+                             float unit_eps, int T, int single, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && C > 0 && taps >= 1 && ld >= C, "conv_silu_unit: bad sizes");
   FB_REQUIRE(n_unit >= 0 && (long long)n_unit * dim <= C && n_scaled <= n_unit,
              "conv_silu_unit: %d unit heads of %d exceed %d channels", n_unit, dim, C);
@@ -415,7 +422,7 @@ FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, int t
                          200 * 1024);
   fb_launch(conv_silu_unit_kernel, dim3(T), dim3(256), smem, stream, x, ld, w, taps, state,
             state_stride, tail_offset, out, C, seq_of_token, cu_tokens, slots, n_unit, dim,
-            n_scaled, extra, unit_eps);
+            n_scaled, extra, unit_eps, single);
   return fb_check_launch("conv_silu_unit");
 }
 

@@ -101,12 +101,12 @@ _SIGNATURES = {
                                     c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int,
                                     c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p],
     "fb_token_shift_mix": [c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
-                           c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "fb_state_tail_update": [c_void_p, c_int, c_ll, c_void_p, c_ll, c_ll, c_int, c_int, c_void_p,
                              c_void_p, c_int, c_void_p],
     "fb_conv_silu_unit": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_int,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
-                          c_int, c_void_p],
+                          c_int, c_int, c_void_p],
     "fb_decay_gate": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "fb_state_scan": [c_int, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll,
                       c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
@@ -1671,9 +1671,11 @@ class StateRows:
 
 
 def token_shift_mix(ctx, h: torch.Tensor, state: StateRows, field: str, mu: torch.Tensor,
-                    out: torch.Tensor) -> torch.Tensor:
+                    out: torch.Tensor) -> bool:
     """out[m, t] = h[t] + (h[t-1] - h[t]) * mu[m]; a sequence's row before the
-    step is state field `field`."""
+    step is state field `field`. In a step of one token a sequence the kernel
+    also leaves the token's row in the state and True comes back; otherwise the
+    caller updates the state afterwards (`state_tail_update`)."""
     T, W = h.shape
     n = mu.shape[0]
     if out.shape != (n, T, W) or mu.shape != (n, W) or out.dtype != h.dtype:
@@ -1682,8 +1684,8 @@ def token_shift_mix(ctx, h: torch.Tensor, state: StateRows, field: str, mu: torc
           state.offset[field], _dev(mu, "mu", torch.float32), _dev(out, "out"),
           _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
           _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.slots, "slots", torch.int32),
-          T, W, n, _stream())
-    return out
+          T, W, n, 1 if ctx.is_decode else 0, _stream())
+    return bool(ctx.is_decode)
 
 
 def state_tail_update(ctx, x: torch.Tensor, state: StateRows, field: str, n_tail: int,
@@ -1698,9 +1700,11 @@ def state_tail_update(ctx, x: torch.Tensor, state: StateRows, field: str, n_tail
 
 def conv_silu_unit(ctx, x: torch.Tensor, weight: torch.Tensor, state: StateRows, field: str,
                    out: torch.Tensor, channels: int, n_unit: int, dim: int, n_scaled: int,
-                   extra: float, unit_eps: float) -> torch.Tensor:
+                   extra: float, unit_eps: float) -> bool:
     """Causal convolution over time per channel, SiLU, then unit-length heads
-    (csrc/sequence_mix.cu). `x` float32 rows (first `channels` columns are used)."""
+    (csrc/sequence_mix.cu). `x` float32 rows (first `channels` columns are used).
+    Returns whether the kernel moved the state's tail on itself (a step of one
+    token a sequence); otherwise `state_tail_update` has to follow."""
     T = x.shape[0]
     taps = weight.shape[1]
     if weight.shape[0] != channels or out.shape != (T, channels):
@@ -1710,8 +1714,9 @@ def conv_silu_unit(ctx, x: torch.Tensor, weight: torch.Tensor, state: StateRows,
           state.offset[field], _dev(out, "out", torch.float32), channels,
           _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
           _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.slots, "slots", torch.int32),
-          n_unit, dim, n_scaled, float(extra), float(unit_eps), T, _stream())
-    return out
+          n_unit, dim, n_scaled, float(extra), float(unit_eps), T, 1 if ctx.is_decode else 0,
+          _stream())
+    return bool(ctx.is_decode)
 
 
 def decay_gate(x: torch.Tensor, per_head: int, bias: torch.Tensor, A: Optional[torch.Tensor]):

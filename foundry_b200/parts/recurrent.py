@@ -92,9 +92,9 @@ class GatedDeltaChannel(Part):
         state = ops.StateRows(cache.rows, self.fields)
         p = product_f32(x, self.w_in)
         qkv = torch.empty((T, C), **f32)
-        ops.conv_silu_unit(ctx, p, self.conv, state, "tail", qkv, C, n_unit=2 * G, dim=d,
-                           n_scaled=G, extra=d ** -0.5, unit_eps=self.unit_eps)
-        ops.state_tail_update(ctx, p, state, "tail", self.taps - 1, C)
+        if not ops.conv_silu_unit(ctx, p, self.conv, state, "tail", qkv, C, n_unit=2 * G, dim=d,
+                                  n_scaled=G, extra=d ** -0.5, unit_eps=self.unit_eps):
+            ops.state_tail_update(ctx, p, state, "tail", self.taps - 1, C)
         low = torch.empty((T, self.decay_rank + self.gate_rank), dtype=x.dtype, device=x.device)
         ops.unary_cast(p[:, C + H:], low)
         decay = product_f32(low[:, :self.decay_rank], self.a2)
@@ -151,8 +151,8 @@ class WkvTimeMix(Part):
         H, d = self.heads, self.dim
         state = ops.StateRows(cache.rows, self.fields)
         mixes = torch.empty((len(self.MIXES), T, W), dtype=x.dtype, device=x.device)
-        ops.token_shift_mix(ctx, x, state, "prev", self.mu, mixes)
-        ops.state_tail_update(ctx, x, state, "prev", 1, W)
+        if not ops.token_shift_mix(ctx, x, state, "prev", self.mu, mixes):
+            ops.state_tail_update(ctx, x, state, "prev", 1, W)
         r, k, v, g = (product_f32(mixes[i], w) for i, w in
                       enumerate((self.r, self.k, self.v, self.g)))
         low = torch.empty((T, self.decay_rank), dtype=x.dtype, device=x.device)

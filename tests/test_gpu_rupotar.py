@@ -396,3 +396,17 @@ def test_trace_replay_and_command_line(folders, tmp_path):
     assert run.returncode == 0, run.stderr[-2000:]
     want = plain.greedy_generate(cfg, double(weights), a, 4)
     assert json.loads(run.stdout.strip().split("\n")[-1]) == want
+
+
+def test_command_line_bench_on_a_rupotar_folder(folders, tmp_path):
+    """`foundry bench` (prompt step, decode steps, report with bytes and operations)
+    on a model with state rows and routed experts."""
+    folder, _ = folders["looped"]
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "foundry"), "bench", "--model",
+                           folder, "--prompt-tokens", "20", "--new-tokens", "5", "--runs", "2",
+                           "--batch-size", "3", "--out", str(tmp_path)],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    report = json.loads((tmp_path / "report.json").read_text())
+    assert len(report["runs"]) == 2 and all(len(r) == 5 for r in report["runs"][0]["token_ids"])
+    assert report["runs"][0]["token_ids"] == report["runs"][1]["token_ids"]
