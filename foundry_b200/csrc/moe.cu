@@ -286,7 +286,7 @@ __device__ __forceinline__ void w8<__nv_bfloat16>(const __nv_bfloat16* __restric
 // 103 us a call at 16 pairs over 16 experts of 2048 x 2048.)
 // `pair_at` given: the sorted row `at` is row pair_at[at] / top of x (no gathered copy).
 template <typename T, typename TX, bool GATED, int CHUNK>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 2)
 moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const int* starts,
                    float* __restrict__ out, long long ldo, int K, int N, int rows_per_block,
                    float limit, float alpha, const int* pair_at, int top) {
@@ -315,16 +315,26 @@ moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const in
       for (int r = 0; r < CHUNK; ++r) acc[r] = acc2[r] = 0.f;
       const T* wr = we + (size_t)row * K;
       const T* wr2 = we + (size_t)(N + row) * K;
-      // two steps of 256 weights at a time: their loads are all issued before the sums
-      for (int k0 = lane * 8; k0 < K; k0 += 512) {
-        float a[2][8], b[2][8];
+      // two steps of 256 weights at a time, read one round ahead: the loads of the next
+      // 512 weights are on their way while the sums over these are made
+      float an[2][8], bn[2][8];
+      auto fetch = [&](int k0) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           if (k0 + u * 256 < K) {
-            w8<T>(wr + k0 + u * 256, a[u]);
-            if (GATED) w8<T>(wr2 + k0 + u * 256, b[u]);
+            w8<T>(wr + k0 + u * 256, an[u]);
+            if (GATED) w8<T>(wr2 + k0 + u * 256, bn[u]);
           }
         }
+      };
+      fetch(lane * 8);
+      for (int k0 = lane * 8; k0 < K; k0 += 512) {
+        float a[2][8], b[2][8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { a[u][e] = an[u][e]; if (GATED) b[u][e] = bn[u][e]; }
+        if (k0 + 512 < K) fetch(k0 + 512);
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int k = k0 + u * 256;
