@@ -372,6 +372,112 @@ moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const in
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same two products on the tensor cores (bfloat16, K a multiple of 64): up to 8
+// input rows of an expert are the 8 columns of `mma.sync.m16n8k16`, 16 weight rows
+// its rows. A warp owns a tile of 16 weight rows (GATED: the 16 gate rows and their 16
+// up rows) and pulls the weights straight from global memory into A fragments: of a
+// block of 64 weights a thread reads the 16 consecutive ones at 16 (lane % 4) of rows
+// lane / 4 and lane / 4 + 8 (32 contiguous bytes a row), which it uses as its
+// fragment elements of four k-steps. The dot product does not care in which order K
+// is walked as long as the input rows are read in the same order, so the B fragment
+// of k-step s is the four inputs at 16 (lane % 4) + 4 s of input row lane / 4, one
+// 8-byte load from shared memory. The next block's weights are read while this
+// block's four instructions run.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2,
+                                               unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, "
+               "{%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int MMA_ROWS = 8;   // input rows a chunk
+constexpr int MMA_PAD = 4;    // elements between input rows in shared memory (bank spread)
+
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_mma_kernel(const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* __restrict__ w,
+                       const int* starts, void* out, long long ldo, int K, int N, float limit,
+                       float alpha, const int* pair_at, int top) {
+  fb_pdl_wait();
+  extern __shared__ __align__(16) __nv_bfloat16 xb[];  // [MMA_ROWS][K + MMA_PAD]
+  const int e = blockIdx.x;
+  const int begin = starts[e], end = starts[e + 1];
+  if (begin >= end) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = (blockIdx.y * 8 + warp) * 16;
+  const bool tile = row0 < N;
+  const int ldxs = K + MMA_PAD;
+  const __nv_bfloat16* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+  // rows past the matrix read its last row; their results are not stored
+  const int ra = min(row0 + g, N - 1), rb = min(row0 + g + 8, N - 1);
+  const uint4* ga = reinterpret_cast<const uint4*>(we + (size_t)ra * K + 16 * t);
+  const uint4* gb = reinterpret_cast<const uint4*>(we + (size_t)rb * K + 16 * t);
+  const uint4* ua = reinterpret_cast<const uint4*>(we + (size_t)(N + ra) * K + 16 * t);
+  const uint4* ub = reinterpret_cast<const uint4*>(we + (size_t)(N + rb) * K + 16 * t);
+  for (int c0 = begin; c0 < end; c0 += MMA_ROWS) {
+    const int nc = min(MMA_ROWS, end - c0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < MMA_ROWS * (K / 8); i += blockDim.x) {
+      const int r = i / (K / 8), k = (i - r * (K / 8)) * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < nc) {
+        const size_t src = pair_at != nullptr ? (size_t)(pair_at[c0 + r] / top) : (size_t)(c0 + r);
+        v = __ldcg(reinterpret_cast<const uint4*>(x + src * ldx + k));
+      }
+      uint2* dst = reinterpret_cast<uint2*>(xb + (size_t)r * ldxs + k);  // rows are 8-byte aligned
+      dst[0] = make_uint2(v.x, v.y);
+      dst[1] = make_uint2(v.z, v.w);
+    }
+    __syncthreads();
+    if (!tile) continue;
+    float cg[4] = {0.f, 0.f, 0.f, 0.f}, cu[4] = {0.f, 0.f, 0.f, 0.f};
+    const __nv_bfloat16* xrow = xb + (size_t)g * ldxs + 16 * t;
+    uint4 na[2], nb[2], nua[2], nub[2];
+    auto fetch = [&](int kb) {  // kb in units of 8 elements (a uint4)
+      na[0] = __ldg(ga + kb); na[1] = __ldg(ga + kb + 1);
+      nb[0] = __ldg(gb + kb); nb[1] = __ldg(gb + kb + 1);
+      if (GATED) {
+        nua[0] = __ldg(ua + kb); nua[1] = __ldg(ua + kb + 1);
+        nub[0] = __ldg(ub + kb); nub[1] = __ldg(ub + kb + 1);
+      }
+    };
+    fetch(0);
+    for (int kb = 0; kb < K; kb += 64) {
+      const unsigned a[8] = {na[0].x, na[0].y, na[0].z, na[0].w, na[1].x, na[1].y, na[1].z, na[1].w};
+      const unsigned b[8] = {nb[0].x, nb[0].y, nb[0].z, nb[0].w, nb[1].x, nb[1].y, nb[1].z, nb[1].w};
+      unsigned p[8], q[8];
+      if (GATED) {
+        p[0] = nua[0].x; p[1] = nua[0].y; p[2] = nua[0].z; p[3] = nua[0].w;
+        p[4] = nua[1].x; p[5] = nua[1].y; p[6] = nua[1].z; p[7] = nua[1].w;
+        q[0] = nub[0].x; q[1] = nub[0].y; q[2] = nub[0].z; q[3] = nub[0].w;
+        q[4] = nub[1].x; q[5] = nub[1].y; q[6] = nub[1].z; q[7] = nub[1].w;
+      }
+      if (kb + 64 < K) fetch((kb + 64) / 8);
+#pragma unroll
+      for (int s2 = 0; s2 < 4; ++s2) {
+        const uint2 xv = *reinterpret_cast<const uint2*>(xrow + kb + 4 * s2);
+        mma_bf16_16816(cg, a[2 * s2], b[2 * s2], a[2 * s2 + 1], b[2 * s2 + 1], xv.x, xv.y);
+        if (GATED) mma_bf16_16816(cu, p[2 * s2], q[2 * s2], p[2 * s2 + 1], q[2 * s2 + 1], xv.x, xv.y);
+      }
+    }
+    // c[0], c[1]: weight row g, input rows 2t and 2t + 1; c[2], c[3]: weight row g + 8
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = row0 + g + (i >> 1) * 8, n = 2 * t + (i & 1);
+      if (row < N && n < nc) {
+        if (GATED)
+          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(c0 + n) * ldo + row] =
+              __float2bfloat16_rn(glu_act(cg[i], cu[i], limit, alpha));
+        else
+          reinterpret_cast<float*>(out)[(size_t)(c0 + n) * ldo + row] = cg[i];
+      }
+    }
+  }
+}
+
 __global__ void moe_combine_kernel(const float* y, const int* place, const float* weights, int top,
                                    float* __restrict__ out, int W) {
   fb_pdl_launch();
@@ -456,6 +562,39 @@ FB_API int fb_moe_grouped(int gated, const void* x, long long ldx, const void* w
 #undef FB_MOE_GROUPED
 #undef FB_MOE_GROUPED_C
   return fb_check_launch("moe_grouped");
+}
+
+// gated = 1: out is bfloat16 activations [pairs, N]; gated = 0: out is float32 [pairs, N].
+FB_API int fb_moe_grouped_mma(int gated, const void* x, long long ldx, const void* w,
+                              const int* starts, void* out, long long ldo, int E, int K, int N,
+                              float limit, float alpha, const int* pair_at, int top,
+                              cudaStream_t stream) {
+  FB_REQUIRE(E > 0 && K > 0 && N > 0 && ldx >= K && ldo >= N, "moe_grouped_mma: bad sizes");
+  FB_REQUIRE(K % 64 == 0 && ldx % 8 == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)x % 16) == 0,
+             "moe_grouped_mma: K = %d must be a multiple of 64 and the rows 16-byte aligned", K);
+  FB_REQUIRE(pair_at == nullptr || top > 0, "moe_grouped_mma: rows by pair need the pairs a token");
+  const size_t smem = (size_t)MMA_ROWS * (K + MMA_PAD) * 2;
+  FB_REQUIRE(smem <= 200 * 1024, "moe_grouped_mma: %d input rows of %d do not fit shared memory",
+             MMA_ROWS, K);
+  dim3 grid(E, (N + 127) / 128);
+  if (gated) {
+    static bool seen[64];
+    if (fb_first_use_on_device(seen))
+      cudaFuncSetAttribute(moe_grouped_mma_kernel<true>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    fb_launch(moe_grouped_mma_kernel<true>, grid, dim3(256), smem, stream,
+              (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, starts, out, ldo, K, N, limit,
+              alpha, pair_at, top);
+  } else {
+    static bool seen[64];
+    if (fb_first_use_on_device(seen))
+      cudaFuncSetAttribute(moe_grouped_mma_kernel<false>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    fb_launch(moe_grouped_mma_kernel<false>, grid, dim3(256), smem, stream,
+              (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, starts, out, ldo, K, N, limit,
+              alpha, pair_at, top);
+  }
+  return fb_check_launch("moe_grouped_mma");
 }
 
 FB_API int fb_moe_combine(const float* y, const int* place, const float* weights, int top,

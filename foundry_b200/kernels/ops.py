@@ -124,6 +124,8 @@ _SIGNATURES = {
                    c_int, c_void_p],
     "fb_moe_grouped": [c_int, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_int,
                        c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_int, c_void_p],
+    "fb_moe_grouped_mma": [c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
+                           c_int, c_float, c_float, c_void_p, c_int, c_void_p],
     "fb_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -1858,6 +1860,33 @@ def moe_grouped(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: boo
           code_of(w.dtype), order.starts.data_ptr(), out.data_ptr(), N, E, K, N, float(limit),
           float(alpha), sm_count(), order.pair_at.data_ptr() if by_token else 0, order.top,
           order.pairs, _stream())
+    return out
+
+
+MOE_GROUPED_MMA = _os.environ.get("FOUNDRY_B200_MOE_GROUPED_MMA", "1") != "0"
+
+
+def moe_grouped_mma_fits(x: torch.Tensor, *ks: int) -> bool:
+    """Whether the tensor-core form takes products over these K: bfloat16, multiples
+    of 64, input rows that fit shared memory."""
+    return (MOE_GROUPED_MMA and x.dtype == torch.bfloat16
+            and all(k % 64 == 0 and 8 * (k + 4) * 2 <= 200 * 1024 for k in ks))
+
+
+def moe_grouped_mma(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: bool,
+                    limit: float = 0.0, alpha: float = 0.0, by_token: bool = False) -> torch.Tensor:
+    """`moe_grouped` on the tensor cores (bfloat16 in; the gated product gives the
+    activations in bfloat16, the other one float32)."""
+    E, rows, K = w.shape
+    N = rows // 2 if gated else rows
+    out = torch.empty((order.pairs, N), dtype=torch.bfloat16 if gated else torch.float32,
+                      device=x.device)
+    if order.pairs == 0:
+        return out
+    _call("fb_moe_grouped_mma", 1 if gated else 0, _dev(x, "x", torch.bfloat16), x.stride(0),
+          _dev(w, "w", torch.bfloat16), order.starts.data_ptr(), out.data_ptr(), N, E, K, N,
+          float(limit), float(alpha), order.pair_at.data_ptr() if by_token else 0, order.top,
+          _stream())
     return out
 
 

@@ -72,6 +72,10 @@ class RoutedExperts(Part):
         order = ops.ExpertOrder(chosen, self.experts)
         if T >= self.LIBRARY_ROWS and getattr(ctx, "cu_tokens_host", None) is not None:
             y = self._per_expert_products(ops.moe_gather(x, order), order)
+        elif ops.moe_grouped_mma_fits(x, self.width, self.ff):
+            act = ops.moe_grouped_mma(x, self.gate_up, order, True, self.limit, self.alpha,
+                                      by_token=True)
+            y = ops.moe_grouped_mma(act, self.down, order, False)
         else:
             act = ops.moe_grouped(x, self.gate_up, order, True, self.limit, self.alpha,
                                   by_token=True)

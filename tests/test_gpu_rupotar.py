@@ -155,6 +155,34 @@ def test_feed_forwards_norm_embedding_and_junction_alone(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens", [1, 5, 40])
+def test_routed_experts_at_sizes_of_the_tensor_core_form(dtype, tokens):
+    """Width 128 and 192 hidden units (multiples of 64): in bfloat16 the grouped
+    products run on the tensor cores; 40 tokens over 6 experts give chunks of more than
+    8 rows, 1 token leaves most experts without any."""
+    from foundry_b200.config.spec import PartSpec
+    from foundry_b200.parts import FEED_FORWARDS
+    W, ff, E, top = 128, 192, 6, 2
+    mlp = {"router": {"experts": E, "top": top}, "expert": {"ff": ff, "limit": 1.2}}
+    gen = torch.Generator().manual_seed(21)
+    weights = {"m.router": torch.randn(E, W, generator=gen) * 0.3,
+               "m.router.b": torch.randn(E, generator=gen) * 0.2}
+    for e in range(E):
+        weights[f"m.e{e}.gate"] = torch.randn(ff, W, generator=gen) * 0.15
+        weights[f"m.e{e}.up"] = torch.randn(ff, W, generator=gen) * 0.15
+        weights[f"m.e{e}.down"] = torch.randn(W, ff, generator=gen) * 0.15
+    weights = {k: v.to(torch.bfloat16).float() for k, v in weights.items()}
+    part = FEED_FORWARDS.build(PartSpec("routed_experts", {
+        "width": W, "ff": ff, "experts": E, "top": top, "limit": 1.2, "alpha": 1.702}),
+        dtype=dtype, device=DEV)
+    part.load("m", lambda n: weights[n].to(DEV).to(dtype if weights[n].dim() > 1 else torch.float32))
+    x = torch.randn(tokens, W, generator=gen).to(dtype)
+    got = part.forward(None, x.to(DEV))
+    want = plain.routed_experts(mlp, double(weights), "m", x.double())
+    assert rel_error(got.float().cpu(), want) < bound(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_with_sizes_that_fit_no_vector(dtype):
     """Key size 12 and value size 20 (no multiple of 8), three heads on one key/value
     head, no window, no kept tokens: the scalar paths of the CUDA-core kernel."""
