@@ -420,7 +420,10 @@ FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, int t
   if (smem > 48 * 1024 && fb_first_use_on_device(seen))
     cudaFuncSetAttribute(conv_silu_unit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          200 * 1024);
-  fb_launch(conv_silu_unit_kernel, dim3(T), dim3(256), smem, stream, x, ld, w, taps, state,
+  // few tokens: wide blocks, so that a token's loads are many threads' and not one
+  // thread's one after another
+  const int threads = (T <= 64 && C >= 2048) ? 1024 : 256;
+  fb_launch(conv_silu_unit_kernel, dim3(T), dim3(threads), smem, stream, x, ld, w, taps, state,
             state_stride, tail_offset, out, C, seq_of_token, cu_tokens, slots, n_unit, dim,
             n_scaled, extra, unit_eps, single);
   return fb_check_launch("conv_silu_unit");
