@@ -135,7 +135,7 @@ struct AttnParams {
   // prompts, masked form only: a key j is seen from position i iff j <= i and
   // (window == 0 or i - j < window or j < keep_first); scores lose
   // 2^(-steep (head + 1) / A) per token of distance (steep 0: no bias); with `sink`
-  // the softmax has one more term of score 0 that carries no value
+  // the softmax's sum has one more term exp(0), which adds nothing to the output
   int window, keep_first, sink;
   float steep;
 };

@@ -6,14 +6,14 @@
 //   k' = k / sqrt(mean(k^2) + eps) * wk     (before the split into heads)
 //   s_ij = (q'_i . k'_j) * scale - slope_h * (i - j),  slope_h = 2^(-steep (h+1) / H)
 //   j visible to i  iff  j <= i and (i - j < window or j < keep_first)
-//   p_ij = exp(s_ij) / (sink + sum_j exp(s_ij)),  sink = 1 or 0: a key of score 0
-//          that has no value
+//   p_ij = exp(s_ij) / (sink + sum_j exp(s_ij)),  sink = 1 or 0: one more term exp(0)
+//          in the sum, which adds nothing to the output
 //   o_i = sum_j p_ij v_j
 //
 // Every constant is a parameter: window 0 = all earlier keys, steep 0 = no bias,
 // sink 0 = the plain softmax. Keys have `dim` elements and values `vdim`; the
-// two caches have strides of their own. Positions are the tokens' own, so a
-// kept token keeps its true distance.
+// two caches have strides of their own. Positions are the tokens' own, so the
+// bias of a kept token is by the distance it really has.
 //
 // This file holds the CUDA-core forms (32-bit arithmetic, any sizes): one warp
 // per (token, query head) walking the kept prefix and then the window.
@@ -143,7 +143,7 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
   const int total = kept + (pos + 1 - lo);
   const int i0 = (int)((long long)total * blockIdx.z / splits);
   const int i1 = (int)((long long)total * (blockIdx.z + 1) / splits);
-  // the sink is a key of score 0 without a value: it starts the running maximum and sum
+  // the sink is the term exp(0) of the sum: the running maximum starts at 0, the sum at 1
   const bool own_sink = mask.sink && splits == 1;
   float m = own_sink ? 0.f : -INFINITY, l = own_sink ? 1.f : 0.f;
   float acc[MAX_D / 32];

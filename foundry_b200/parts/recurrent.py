@@ -4,7 +4,8 @@
 
     q = Wq h, k = Wk h  (kv_heads x dim),  v = Wv h  (heads x vdim); head a uses q/k head
     a // (heads / kv_heads). Each passes a causal convolution over time per channel
-    (taps weights, the last one the current token's, zeros before the start) and SiLU;
+    (`taps` weights a channel, the newest input under the last weight, nothing but zeros in
+    front of a sequence's first token) and SiLU;
     q and k become unit vectors per head, x / sqrt(sum x^2 + 1e-6), q also times dim^-1/2.
     beta = sigmoid(Wb h) per head;  g = exp(-exp(A_log[a]) softplus(Wa2 (Wa1 h) + dt_bias))
     per head and key channel.

@@ -5,11 +5,11 @@ the first tokens, and a softmax with a sink, as a mixer.
     q, k: RMS norm over the WHOLE projection of a token (all heads at once), weights wq, wk
     s_ij = (q_i . k_j) * scale - slope_h (i - j),   slope_h = 2^(-steep (h + 1) / heads)
     j visible to i iff j <= i and (i - j < window or j < keep_first)
-    p_ij = exp(s_ij) / (1 + sum_j exp(s_ij))        (the 1: a sink of score 0 without a value)
+    p_ij = exp(s_ij) / (1 + sum_j exp(s_ij))        (the 1 is exp(0): one more term in the sum that adds nothing to the output)
     out = Wo [heads' outputs side by side]
 
 Keys have `dim` elements a head, values `vdim`. No rotation: positions enter
-through the bias and the mask only, and a kept token keeps its true distance.
+through the bias and the mask only; the bias of a kept token is by the distance it really has.
 Every constant (scale, steep, window, keep_first, the sink) is a parameter; the
 tensor names under the mixer's prefix are `q k v o` and `q.norm k.norm` unless
 given otherwise.

@@ -100,7 +100,7 @@ def test_plain_recurrent_mixers_equal_their_stepwise_forms(name):
 
 def test_plain_attention_mask_sink_and_bias():
     """One query over three keys by hand: the sink's one in the denominator, the
-    bias by true distance, the window with a kept first token."""
+    bias by the tokens' own distance, the window with a kept first token."""
     m = {"heads": 1, "kv_heads": 1, "dim": 2, "vdim": 1, "scale": 1.0,
          "mask": {"size": 2, "keep_first": 1}}
     eye = torch.eye(2, dtype=torch.float64)
