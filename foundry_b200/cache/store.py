@@ -30,7 +30,9 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None  # None: every earlier position stays readable
-    v_head_dim: Optional[int] = None  # None: values have the keys' size
+    # None: values have the keys' size; 0: no value rows are stored (a mixer whose
+    # values are a part of its key rows; both views of the entry are the key rows)
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -50,7 +52,12 @@ class KVGroup:
         self.index_of = {e: i for i, e in enumerate(entries)}
         self.pages = GroupPages(page_count, request.window)
         self.v_storage = None
-        if request.v_head_dim in (None, request.head_dim):
+        self.keys_only = request.v_head_dim == 0
+        if self.keys_only:
+            self.storage = torch.zeros(
+                (len(entries), page_count, request.kv_heads, PAGE, request.head_dim),
+                dtype=dtype, device=device)
+        elif request.v_head_dim in (None, request.head_dim):
             self.storage = torch.zeros(
                 (len(entries), page_count, 2, request.kv_heads, PAGE, request.head_dim),
                 dtype=dtype, device=device)
@@ -75,7 +82,9 @@ class KVGroup:
         views = self._views.get(entry)
         if views is None:  # the views never change: made once per entry
             block = self.storage[self.index_of[entry]]
-            if self.v_storage is None:
+            if self.keys_only:
+                views = self._views[entry] = (block, block)
+            elif self.v_storage is None:
                 views = self._views[entry] = (block[:, 0], block[:, 1])
             else:
                 views = self._views[entry] = (block, self.v_storage[self.index_of[entry]])
@@ -83,8 +92,8 @@ class KVGroup:
 
     def bytes_per_token(self) -> int:
         r = self.request
-        return (len(self.entries) * r.kv_heads * (r.head_dim + (r.v_head_dim or r.head_dim))
-                * self.storage.element_size())
+        v = r.head_dim if r.v_head_dim is None else r.v_head_dim
+        return len(self.entries) * r.kv_heads * (r.head_dim + v) * self.storage.element_size()
 
 
 @dataclass

@@ -117,7 +117,7 @@ template <typename TD, typename TO, int ITEMS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* delta,
                                        int planes, long long plane_stride,
                                        const float* __restrict__ weight, TO* __restrict__ out,
-                                       int H, float eps, float inv_h) {
+                                       int H, float eps, float inv_h, float dscale) {
   fb_pdl_launch();
   fb_pdl_wait();
   __shared__ float scratch[32];
@@ -145,7 +145,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* delt
       const int i = (threadIdx.x + it * blockDim.x) * 4;
       if (i < H) {
         const float4 add = widen(raw[it]);
-        v[it].x += add.x; v[it].y += add.y; v[it].z += add.z; v[it].w += add.w;
+        v[it].x = fmaf(dscale, add.x, v[it].x); v[it].y = fmaf(dscale, add.y, v[it].y);
+        v[it].z = fmaf(dscale, add.z, v[it].z); v[it].w = fmaf(dscale, add.w, v[it].w);
         store4<float>(x + i, v[it]);
         ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
       }
@@ -170,7 +171,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* delt
           for (int s = 1; s < 8; ++s) {
             add.x += part[s].x; add.y += part[s].y; add.z += part[s].z; add.w += part[s].w;
           }
-          v[it].x += add.x; v[it].y += add.y; v[it].z += add.z; v[it].w += add.w;
+          v[it].x = fmaf(dscale, add.x, v[it].x); v[it].y = fmaf(dscale, add.y, v[it].y);
+          v[it].z = fmaf(dscale, add.z, v[it].z); v[it].w = fmaf(dscale, add.w, v[it].w);
         }
         store4<float>(x + i, v[it]);
       }
@@ -197,7 +199,7 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* delta,
                                    int planes, long long plane_stride,
                                    const float* __restrict__ weight, TO* __restrict__ out, int H,
-                                   float eps, float inv_h) {
+                                   float eps, float inv_h, float dscale) {
   fb_pdl_launch();
   fb_pdl_wait();
   __shared__ float scratch[32];
@@ -209,7 +211,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* delta,
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float add = fb_to_float<TD>(d[i]);
       for (int s = 1; s < planes; ++s) add += fb_to_float<TD>(d[(size_t)s * plane_stride + i]);
-      const float v = x[i] + add;
+      const float v = fmaf(dscale, add, x[i]);
       x[i] = v;
       ss += v * v;
     }
@@ -230,7 +232,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* delta,
 
 FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int planes,
                           long long plane_stride, const float* weight, float eps, void* out,
-                          int out_dtype, int T, int H, cudaStream_t stream) {
+                          int out_dtype, int T, int H, float delta_scale, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && H > 0, "add_rmsnorm: bad sizes T=%d H=%d", T, H);
   FB_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
   FB_REQUIRE(planes >= 1 && (planes == 1 || delta_dtype == FB_F32),
@@ -254,7 +256,7 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
 #define FB_NORM_LAUNCH(N)                                                                     \
     FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (                     \
         fb_launch(add_rmsnorm_vec_kernel<TD, TO, N>, dim3(T), dim3(threads), 0, stream,                          \
-            resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h))))
+            resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h, delta_scale))))
     if (items <= 1) { FB_NORM_LAUNCH(1); }
     else if (items == 2) { FB_NORM_LAUNCH(2); }
     else { FB_NORM_LAUNCH(4); }
@@ -264,7 +266,7 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (
       fb_launch(add_rmsnorm_kernel<TD, TO>, dim3(T), dim3(threads), 0, stream, 
-          resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h))));
+          resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h, delta_scale))));
   return fb_check_launch("add_rmsnorm");
 }
 
@@ -335,32 +337,36 @@ FB_API int fb_row_scales(const float* shares, int count, int stride, int dim, fl
 // gate_up is [T, 2I]. Plain layout: columns [0, I) hold the gate, [I, 2I) the
 // up projection. Interleaved layout: column 2i holds gate i, column 2i+1 up i
 // (the layout the fused product epilogue uses).
-template <typename T>
-__global__ void silu_mul_kernel(const T* gate_up, T* __restrict__ out, int I,
-                                size_t total, int interleaved) {
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(const TI* gate_up, TO* __restrict__ out, int I,
+                                size_t total, int interleaved, int act) {
   fb_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
-    const T* row = gate_up + t * 2 * I;
-    const float g = fb_to_float<T>(interleaved ? row[2 * i] : row[i]);
-    const float u = fb_to_float<T>(interleaved ? row[2 * i + 1] : row[I + i]);
-    const float a = g / (1.0f + expf(-g));
-    out[idx] = fb_from_float<T>(a * u);
+    const TI* row = gate_up + t * 2 * I;
+    const float g = fb_load_coherent<TI>(interleaved ? row + 2 * i : row + i);
+    const float u = fb_load_coherent<TI>(interleaved ? row + 2 * i + 1 : row + I + i);
+    // act 0: SiLU; 1: the tanh form of GELU, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+    const float a = act == 0 ? g / (1.0f + expf(-g))
+                             : 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    out[idx] = fb_from_float<TO>(a * u);
   }
 }
 
-FB_API int fb_silu_mul(const void* gate_up, void* out, int dtype, int T, int I, int interleaved,
-                       cudaStream_t stream) {
+FB_API int fb_silu_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int T, int I,
+                       int interleaved, int act, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T, I);
+  FB_REQUIRE(act == 0 || act == 1, "silu_mul: unknown activation %d", act);
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   const int threads = 256;
   const size_t want = (total + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(silu_mul_kernel<E>, dim3(blocks), dim3(threads), 0, stream, 
-                                  (const E*)gate_up, (E*)out, I, total, interleaved)));
+  FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, TO, (
+      fb_launch(silu_mul_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream,
+                (const TI*)gate_up, (TO*)out, I, total, interleaved, act))));
   return fb_check_launch("silu_mul");
 }
 

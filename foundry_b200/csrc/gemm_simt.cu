@@ -16,8 +16,14 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TI* x /* written by the kernel before: no read-only promise */,
                  const TI* __restrict__ w, TO* __restrict__ out, int M,
-                 int N, int K, long long ldx, long long ldw, long long ldo) {
+                 int N, int K, long long ldx, long long ldw, long long ldo, long long bx,
+                 long long bw, long long bo) {
   fb_pdl_wait();
+  // blockIdx.z: one of several products of the same sizes whose operands lie
+  // bx / bw / bo elements apart (the heads of a per-head projection)
+  x += (long long)blockIdx.z * bx;
+  w += (long long)blockIdx.z * bw;
+  out += (long long)blockIdx.z * bo;
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -77,6 +83,24 @@ FB_API int fb_gemm_simt(const void* x, const void* w, void* out, int M, int N, i
   FB_REQUIRE(grid.y <= 65535, "gemm_simt: M=%d exceeds the grid limit", M);
   FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, TO, (
       fb_launch(gemm_simt_kernel<TI, TO>, dim3(grid), dim3(256), 0, stream, 
-          (const TI*)x, (const TI*)w, (TO*)out, M, N, K, ldx, ldw, ldo))));
+          (const TI*)x, (const TI*)w, (TO*)out, M, N, K, ldx, ldw, ldo, 0LL, 0LL, 0LL))));
   return fb_check_launch("gemm_simt");
+}
+
+// `count` products of the same sizes in one launch: product b reads x + b * bx and
+// w + b * bw and writes out + b * bo (elements). Each sums as the single product does.
+FB_API int fb_gemm_simt_batched(const void* x, const void* w, void* out, int M, int N, int K,
+                                long long ldx, long long ldw, long long ldo, int count,
+                                long long bx, long long bw, long long bo, int in_dtype,
+                                int out_dtype, cudaStream_t stream) {
+  FB_REQUIRE(M >= 0 && N > 0 && K > 0 && count > 0 && count <= 65535,
+             "gemm_simt_batched: bad sizes M=%d N=%d K=%d count=%d", M, N, K, count);
+  FB_REQUIRE(ldx >= K && ldw >= K && ldo >= N, "gemm_simt_batched: a leading dimension is too small");
+  if (M == 0) return 0;
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, count);
+  FB_REQUIRE(grid.y <= 65535, "gemm_simt_batched: M=%d exceeds the grid limit", M);
+  FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, TO, (
+      fb_launch(gemm_simt_kernel<TI, TO>, dim3(grid), dim3(256), 0, stream,
+          (const TI*)x, (const TI*)w, (TO*)out, M, N, K, ldx, ldw, ldo, bx, bw, bo))));
+  return fb_check_launch("gemm_simt_batched");
 }

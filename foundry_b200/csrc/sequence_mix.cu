@@ -135,18 +135,21 @@ __global__ void conv_silu_unit_kernel(const float* x, long long ld, const float*
 }
 
 // -------------------------------------------------------------------- decays
-// mode 0: x <- exp(-exp(A[head]) * softplus(x + bias[c]))   (c = head * per_head + channel)
-// mode 1: x <- exp(-exp(x + bias[c]))
-__global__ void decay_gate_kernel(float* x, long long n_total, int n, int per_head,
-                                  const float* __restrict__ A, const float* __restrict__ bias,
-                                  int mode) {
+// mode 0: out <- exp(-exp(A[head]) * softplus(x + bias[c]))   (c = head * per_head + channel;
+//         per_head = 1: one decay a head)
+// mode 1: out <- exp(-exp(x + bias[c]))
+// x has rows of stride ld, out is contiguous [T, n] (and may be x itself).
+__global__ void decay_gate_kernel(const float* in, long long ld, float* out, long long n_total,
+                                  int n, int per_head, const float* __restrict__ A,
+                                  const float* __restrict__ bias, int mode) {
   fb_pdl_launch();
   fb_pdl_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_total;
        i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(i % n);
-    const float v = x[i] + bias[c];
-    x[i] = mode == 0 ? expf(-expf(A[c / per_head]) * softplusf_(v)) : expf(-expf(v));
+    const long long t = i / n;
+    const int c = (int)(i - t * n);
+    const float v = __ldcg(in + t * ld + c) + bias[c];
+    out[i] = mode == 0 ? expf(-expf(A[c / per_head]) * softplusf_(v)) : expf(-expf(v));
   }
 }
 
@@ -157,13 +160,14 @@ struct ScanArgs {
   const float* q; long long q_ld;   // [T, *]: query (delta) or receptance (wkv); head h at (h / rep) * dim
   const float* k; long long k_ld;   // keys, same head mapping
   const float* v; long long v_ld;   // values: head h at h * vdim
-  const float* g; long long g_ld;   // decays: head h at h * dim
+  const float* g; long long g_ld;   // decays: head h at h * dim, or one per head at h (g_scalar)
   const float* beta; long long beta_ld;  // delta: raw step size per head (sigmoid applied here)
   const float* bonus;               // wkv: [H, dim]
   float* state; long long state_stride; long long s_offset;
   float* out;                       // [T, H * vdim]
   const int* cu_tokens; const int* slots;
   int H, rep, dim, vdim;
+  int g_scalar;                     // one decay a head instead of one a key channel
 };
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
@@ -225,7 +229,8 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
     if (c < 3 * dimp) {
       const int which = c / dimp, row = c - which * dimp;
       if (row < dim) {
-        src = which == 0 ? a.q + qoff + row : which == 1 ? a.k + qoff + row : a.g + goff + row;
+        src = which == 0 ? a.q + qoff + row : which == 1 ? a.k + qoff + row
+                         : a.g_scalar ? a.g + h : a.g + goff + row;
         step = which == 0 ? a.q_ld : which == 1 ? a.k_ld : a.g_ld;
       }
     } else if (c < 3 * dimp + cols_blk) {
@@ -429,15 +434,15 @@ FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, int t
   return fb_check_launch("conv_silu_unit");
 }
 
-FB_API int fb_decay_gate(float* x, int T, int n, int per_head, const float* A, const float* bias,
-                         int mode, cudaStream_t stream) {
-  FB_REQUIRE(T >= 0 && n > 0 && per_head > 0 && bias != nullptr && (mode == 1 || A != nullptr),
-             "decay_gate: bad arguments");
+FB_API int fb_decay_gate(const float* x, long long ld, float* out, int T, int n, int per_head,
+                         const float* A, const float* bias, int mode, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && n > 0 && per_head > 0 && bias != nullptr && (mode == 1 || A != nullptr) &&
+             ld >= n, "decay_gate: bad arguments");
   if (T == 0) return 0;
   const long long total = (long long)T * n;
   const int blocks = (int)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048);
-  fb_launch(decay_gate_kernel, dim3(blocks), dim3(256), 0, stream, x, total, n, per_head, A, bias,
-            mode);
+  fb_launch(decay_gate_kernel, dim3(blocks), dim3(256), 0, stream, x, ld, out, total, n, per_head,
+            A, bias, mode);
   return fb_check_launch("decay_gate");
 }
 
@@ -446,7 +451,7 @@ FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* 
                          const float* beta, long long beta_ld, const float* bonus, float* state,
                          long long state_stride, long long s_offset, float* out,
                          const int* cu_tokens, const int* slots, int n_seqs, int H, int rep,
-                         int dim, int vdim, cudaStream_t stream) {
+                         int dim, int vdim, int g_scalar, cudaStream_t stream) {
   FB_REQUIRE(mode == 0 || mode == 1, "state_scan: unknown recurrence %d", mode);
   FB_REQUIRE(n_seqs >= 0 && H > 0 && rep > 0 && H % rep == 0 && dim > 0 && vdim > 0,
              "state_scan: bad sizes");
@@ -454,7 +459,7 @@ FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* 
   FB_REQUIRE(mode == 0 ? beta != nullptr : bonus != nullptr, "state_scan: a missing input");
   if (n_seqs == 0) return 0;
   ScanArgs a{q, q_ld, k, k_ld, v, v_ld, g, g_ld, beta, beta_ld, bonus, state, state_stride,
-             s_offset, out, cu_tokens, slots, H, rep, dim, vdim};
+             s_offset, out, cu_tokens, slots, H, rep, dim, vdim, g_scalar ? 1 : 0};
   // a column is shared by kp lanes: eight key rows a lane where the head allows it
   // (a token's step is a chain of dependent instructions; fewer rows a lane shorten it)
   int kp = 1;

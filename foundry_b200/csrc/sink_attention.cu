@@ -21,7 +21,7 @@
 
 namespace {
 constexpr int WARPS = 4;
-constexpr int MAX_D = 256;
+constexpr int MAX_QD = 1024;  // elements of a query head over all its maps
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
@@ -95,27 +95,45 @@ __global__ void qk_norm_cache_kernel(const float* qkv, long long ld, T* __restri
 }
 
 // ---------------------------------------------------------------- attention
-struct SinkMask {
+// How a score is made and what joins the softmax's sum, all as parameters:
+//   s = cap(q . k * scale) - slope_h * (i - j),   cap(x) = softcap * tanh(x / softcap) (softcap 0: x)
+//   sink 0: none; 1: one more term exp(0); 2: one more term exp(sink_logit[head])
+// With two maps (MAPS = 2) a query head has two query vectors and a key row two key
+// vectors side by side, [map 1 | map 2]; each map is an attention of its own over the
+// same value rows, and the head's output is
+//   o = a1 - lambda * a2;   o <- o / sqrt(mean(o^2) + post_eps) * post_scale.
+struct ScoreRule {
   int window, keep_first, sink;
-  float scale, steep;
+  const float* sink_logit;
+  float scale, steep, softcap;
+  float lambda, post_eps, post_scale;
 };
 
+__device__ __forceinline__ float capped(float s, float cap) {
+  return cap > 0.f ? cap * tanhf(s / cap) : s;
+}
+
+// Value rows lie `v_row` elements apart and key rows `k_row` (so values may be a
+// part of the key rows: a cache of latent rows read as keys and as values).
 // VEC (value size a multiple of 8, 16-byte aligned value rows): a value row is
 // read as 16-byte pieces by `lpr` neighbouring lanes and 32 / lpr keys are worked at
 // a time, every lane's loads of a chunk independent of one another; the lanes that
-// share a piece add their sums up once, at the end. Otherwise a lane owns the
-// elements lane, lane + 32, ... and keys go one by one.
-template <typename T, bool VEC>
+// share a piece add their sums up once, at the end. Rows of more than 256 values
+// take several pieces a lane (NACC / 8). Otherwise a lane owns the elements lane,
+// lane + 32, ... and keys go one by one. NACC: value elements a lane accumulates.
+template <typename T, bool VEC, int MAPS, int NACC>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long long out_stride,
                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                       const int* __restrict__ page_table, int max_pages, const T* k_cache,
                       const T* v_cache, long long k_page, long long k_head, long long v_page,
-                      long long v_head, SinkMask mask, int H, int G, int D, int VD, int splits,
-                      float* __restrict__ partial, int lpr, int kvec) {
+                      long long v_head, int k_row, int v_row, ScoreRule rule, int H, int G, int D,
+                      int VD, int splits, float* __restrict__ partial, int lpr, int kvec) {
   fb_pdl_wait();
-  __shared__ float qs[WARPS][MAX_D];
+  extern __shared__ float qs_all[];  // [WARPS][MAPS * D]
+  constexpr int PIECES = NACC / 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* qs = qs_all + (size_t)warp * MAPS * D;
   const int t = blockIdx.x;
   const int a = blockIdx.y * WARPS + warp;
   if (a >= H) return;
@@ -127,85 +145,115 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
   }
   const int pos = positions[t];
   const int g = a / (H / G);
-  const T* qrow = q + (size_t)t * q_stride + (size_t)a * D;
-  for (int d = lane; d < D; d += 32) qs[warp][d] = fb_load_coherent<T>(qrow + d);
+  const T* qrow = q + (size_t)t * q_stride + (size_t)a * MAPS * D;
+  for (int d = lane; d < MAPS * D; d += 32) qs[d] = fb_load_coherent<T>(qrow + d);
   __syncwarp();
-  const float slope = mask.steep > 0.f ? exp2f(-mask.steep * (float)(a + 1) / (float)H) : 0.f;
-  const int lo = (mask.window > 0 && pos - mask.window + 1 > 0) ? pos - mask.window + 1 : 0;
-  const int kept = min(mask.keep_first, lo);  // keys [0, kept) lie in front of the window
+  const float slope = rule.steep > 0.f ? exp2f(-rule.steep * (float)(a + 1) / (float)H) : 0.f;
+  const int lo = (rule.window > 0 && pos - rule.window + 1 > 0) ? pos - rule.window + 1 : 0;
+  const int kept = min(rule.keep_first, lo);  // keys [0, kept) lie in front of the window
   const int* pages = page_table + (size_t)seq * max_pages;
   const T* kbase = k_cache + (long long)g * k_head;
   const T* vbase = v_cache + (long long)g * v_head;
 
   // With `splits` > 1 the visible keys (the kept ones, then the window's) are cut into
-  // that many runs; block z takes run z and leaves (max, sum, weighted values) for
-  // `attention_sink_merge_kernel`, which also adds the sink.
+  // that many runs; block z takes run z and leaves (max, sum, weighted values) per map
+  // for `attention_sink_merge_kernel`, which also adds the sink and combines the maps.
   const int total = kept + (pos + 1 - lo);
   const int i0 = (int)((long long)total * blockIdx.z / splits);
   const int i1 = (int)((long long)total * (blockIdx.z + 1) / splits);
-  // the sink is the term exp(0) of the sum: the running maximum starts at 0, the sum at 1
-  const bool own_sink = mask.sink && splits == 1;
-  float m = own_sink ? 0.f : -INFINITY, l = own_sink ? 1.f : 0.f;
-  float acc[MAX_D / 32];
+  // the sink is one more term of the sum: the running maximum starts at its score, the sum at 1
+  const bool own_sink = rule.sink && splits == 1;
+  const float sink_score = rule.sink == 2 ? rule.sink_logit[a] : 0.f;
+  float m[MAPS], l[MAPS];
+  float acc[MAPS][NACC];
 #pragma unroll
-  for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
+  for (int mm = 0; mm < MAPS; ++mm) {
+    m[mm] = own_sink ? sink_score : -INFINITY;
+    l[mm] = own_sink ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[mm][i] = 0.f;
+  }
 
   for (int range = 0; range < 2; ++range) {
     const int begin = range == 0 ? min(i0, kept) : lo + max(i0 - kept, 0);
     const int end = range == 0 ? min(i1, kept) : lo + max(i1 - kept, 0);  // exclusive
     for (int j0 = begin; j0 < end; j0 += 32) {
       const int j = j0 + lane;
-      float s = -INFINITY;
-      long long k_off = 0, v_off = 0;
+      float s[MAPS];
+#pragma unroll
+      for (int mm = 0; mm < MAPS; ++mm) s[mm] = -INFINITY;
+      long long v_off = 0;
       if (j < end) {
         const long long page = pages[j / FB_PAGE];
         const int r = j % FB_PAGE;
-        k_off = page * k_page + (long long)r * D;
-        v_off = page * v_page + (long long)r * VD;
-        const T* krow = kbase + k_off;
-        float dot = 0.f;
-        if (kvec) {  // key rows of whole 16-byte pieces
-          for (int d = 0; d < D; d += 8) {
-            float kv[8];
-            load8<T>(krow + d, kv);
+        v_off = page * v_page + (long long)r * v_row;
+        const T* krow = kbase + page * k_page + (long long)r * k_row;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) dot = fmaf(qs[warp][d + e], kv[e], dot);
+        for (int mm = 0; mm < MAPS; ++mm) {
+          const float* qm = qs + mm * D;
+          const T* km = krow + mm * D;
+          float dot = 0.f;
+          if (kvec) {  // key rows of whole 16-byte pieces
+            for (int d = 0; d < D; d += 8) {
+              float kv[8];
+              load8<T>(km + d, kv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) dot = fmaf(qm[d + e], kv[e], dot);
+            }
+          } else {
+            for (int d = 0; d < D; ++d) dot = fmaf(qm[d], fb_load_coherent<T>(km + d), dot);
           }
-        } else {
-          for (int d = 0; d < D; ++d) dot = fmaf(qs[warp][d], fb_load_coherent<T>(krow + d), dot);
+          s[mm] = capped(dot * rule.scale, rule.softcap) - slope * (float)(pos - j);
         }
-        s = dot * mask.scale - slope * (float)(pos - j);
       }
-      const float m_new = fmaxf(m, fb_warp_max(s));
-      const float corr = expf(m - m_new);  // exp(-inf) = 0 on a first chunk without sink
-      const float p = (j < end) ? expf(s - m_new) : 0.f;
-      l = l * corr + fb_warp_sum(p);
-      m = m_new;
+      float p[MAPS];
 #pragma unroll
-      for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= corr;
+      for (int mm = 0; mm < MAPS; ++mm) {
+        const float m_new = fmaxf(m[mm], fb_warp_max(s[mm]));
+        const float corr = expf(m[mm] - m_new);  // exp(-inf) = 0 on a first chunk without sink
+        p[mm] = (j < end) ? expf(s[mm] - m_new) : 0.f;
+        l[mm] = l[mm] * corr + fb_warp_sum(p[mm]);
+        m[mm] = m_new;
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[mm][i] *= corr;
+      }
       const int n = min(32, end - j0);
       if (VEC) {
-        const int d0 = (lane % lpr) * 8, sub = lane / lpr, ks = 32 / lpr;
+        const int sub = lane / lpr, ks = 32 / lpr;
         for (int jj = 0; jj < n; jj += ks) {  // uniform trip count; lanes past n add nothing
           const int key = jj + sub;
-          const float pj = __shfl_sync(0xffffffffu, p, key & 31);
-          const long long off = __shfl_sync(0xffffffffu, v_off, key & 31);
-          if (key < n && d0 < VD) {
-            float vv[8];
-            load8<T>(vbase + off + d0, vv);
+          float pj[MAPS];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = fmaf(pj, vv[e], acc[e]);
+          for (int mm = 0; mm < MAPS; ++mm) pj[mm] = __shfl_sync(0xffffffffu, p[mm], key & 31);
+          const long long off = __shfl_sync(0xffffffffu, v_off, key & 31);
+#pragma unroll
+          for (int pc = 0; pc < PIECES; ++pc) {
+            const int d0 = ((lane % lpr) + pc * lpr) * 8;
+            if (key < n && d0 < VD) {
+              float vv[8];
+              load8<T>(vbase + off + d0, vv);
+#pragma unroll
+              for (int mm = 0; mm < MAPS; ++mm)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[mm][pc * 8 + e] = fmaf(pj[mm], vv[e], acc[mm][pc * 8 + e]);
+            }
           }
         }
       } else {
         for (int jj = 0; jj < n; ++jj) {
-          const float pj = __shfl_sync(0xffffffffu, p, jj);
+          float pj[MAPS];
+#pragma unroll
+          for (int mm = 0; mm < MAPS; ++mm) pj[mm] = __shfl_sync(0xffffffffu, p[mm], jj);
           const long long off = __shfl_sync(0xffffffffu, v_off, jj);
           const T* vrow = vbase + off;
 #pragma unroll
-          for (int i = 0; i < MAX_D / 32; ++i) {
+          for (int i = 0; i < NACC; ++i) {
             const int d = lane + 32 * i;
-            if (d < VD) acc[i] = fmaf(pj, fb_load_coherent<T>(vrow + d), acc[i]);
+            if (d < VD) {
+              const float vv = fb_load_coherent<T>(vrow + d);
+#pragma unroll
+              for (int mm = 0; mm < MAPS; ++mm) acc[mm][i] = fmaf(pj[mm], vv, acc[mm][i]);
+            }
           }
         }
       }
@@ -214,77 +262,246 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
   if (VEC) {
     // the lanes that hold the same piece of the row (one per key worked at a time)
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
-      for (int off = lpr; off < 32; off <<= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
-    const int d0 = lane * 8;  // after the sum every group of lpr lanes holds the whole row
-    if (splits > 1) {
-      float* dst = partial + (((size_t)t * H + a) * splits + blockIdx.z) * (VD + 2);
-      if (lane == 0) { dst[0] = m; dst[1] = l; }
-      if (lane < lpr && d0 < VD)
+    for (int mm = 0; mm < MAPS; ++mm)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dst[2 + d0 + e] = acc[e];
-      return;
-    }
-    const float inv = 1.0f / l;
-    if (lane < lpr && d0 < VD)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) o[d0 + e] = fb_from_float<T>(acc[e] * inv);
-    return;
+      for (int e = 0; e < NACC; ++e)
+        for (int off = lpr; off < 32; off <<= 1)
+          acc[mm][e] += __shfl_xor_sync(0xffffffffu, acc[mm][e], off);
   }
+  // where the lane's accumulator i lies in the row, and whether this lane is the one to write it
+  auto place = [&](int i) { return VEC ? ((lane % lpr) + (i / 8) * lpr) * 8 + (i % 8) : lane + 32 * i; };
+  const bool writer = !VEC || lane < lpr;
   if (splits > 1) {
-    float* dst = partial + (((size_t)t * H + a) * splits + blockIdx.z) * (VD + 2);
-    if (lane == 0) { dst[0] = m; dst[1] = l; }
 #pragma unroll
-    for (int i = 0; i < MAX_D / 32; ++i) {
-      const int d = lane + 32 * i;
-      if (d < VD) dst[2 + d] = acc[i];
+    for (int mm = 0; mm < MAPS; ++mm) {
+      float* dst = partial + ((((size_t)t * H + a) * splits + blockIdx.z) * MAPS + mm) * (VD + 2);
+      if (lane == 0) { dst[0] = m[mm]; dst[1] = l[mm]; }
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) {
+        const int d = place(i);
+        if (writer && d < VD) dst[2 + d] = acc[mm][i];
+      }
     }
     return;
   }
-  const float inv_l = 1.0f / l;
+  if (MAPS == 1) {
+    const float inv_l = 1.0f / l[0];
 #pragma unroll
-  for (int i = 0; i < MAX_D / 32; ++i) {
-    const int d = lane + 32 * i;
-    if (d < VD) o[d] = fb_from_float<T>(acc[i] * inv_l);
+    for (int i = 0; i < NACC; ++i) {
+      const int d = place(i);
+      if (writer && d < VD) o[d] = fb_from_float<T>(acc[0][i] * inv_l);
+    }
+    return;
+  }
+  const float inv0 = 1.0f / l[0], inv1 = 1.0f / l[MAPS - 1];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NACC; ++i) {
+    const int d = place(i);
+    acc[0][i] = acc[0][i] * inv0 - rule.lambda * (acc[MAPS - 1][i] * inv1);
+    if (writer && d < VD) ss = fmaf(acc[0][i], acc[0][i], ss);
+  }
+  const float r = rule.post_scale / sqrtf(fb_warp_sum(ss) / (float)VD + rule.post_eps);
+#pragma unroll
+  for (int i = 0; i < NACC; ++i) {
+    const int d = place(i);
+    if (writer && d < VD) o[d] = fb_from_float<T>(acc[0][i] * r);
   }
 }
 
 // One warp per (token, head): the runs' partial results become the output.
-template <typename T>
+template <typename T, int MAPS, int NACC>
 __global__ void attention_sink_merge_kernel(const float* partial, T* __restrict__ out,
                                             long long out_stride, const int* __restrict__ seq_of_token,
-                                            int H, int VD, int splits, int sink) {
+                                            int H, int VD, int splits, ScoreRule rule) {
   fb_pdl_launch();
   fb_pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x, a = blockIdx.y * WARPS + warp;
   if (a >= H || seq_of_token[t] < 0) return;  // padding rows were written by the first kernel
-  const float* src = partial + ((size_t)t * H + a) * splits * (VD + 2);
-  float M = sink ? 0.f : -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(src + (size_t)s * (VD + 2)));
-  float L = sink ? expf(-M) : 0.f;
-  float acc[MAX_D / 32];
+  const float sink_score = rule.sink == 2 ? rule.sink_logit[a] : 0.f;
+  float acc[MAPS][NACC];
 #pragma unroll
-  for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float* ps = src + (size_t)s * (VD + 2);
-    const float ms = __ldcg(ps);
-    if (ms == -INFINITY) continue;  // an empty run
-    const float f = expf(ms - M);
-    L = fmaf(__ldcg(ps + 1), f, L);
+  for (int mm = 0; mm < MAPS; ++mm) {
+    const float* src = partial + (((size_t)t * H + a) * splits * MAPS + mm) * (VD + 2);
+    const size_t step = (size_t)MAPS * (VD + 2);  // from one run's record of this map to the next
+    float M = rule.sink ? sink_score : -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(src + s * step));
+    float L = rule.sink ? expf(sink_score - M) : 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_D / 32; ++i) {
-      const int d = lane + 32 * i;
-      if (d < VD) acc[i] = fmaf(__ldcg(ps + 2 + d), f, acc[i]);
+    for (int i = 0; i < NACC; ++i) acc[mm][i] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* ps = src + s * step;
+      const float ms = __ldcg(ps);
+      if (ms == -INFINITY) continue;  // an empty run
+      const float f = expf(ms - M);
+      L = fmaf(__ldcg(ps + 1), f, L);
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < VD) acc[mm][i] = fmaf(__ldcg(ps + 2 + d), f, acc[mm][i]);
+      }
     }
-  }
-  const float inv = 1.0f / L;
-  T* o = out + (size_t)t * out_stride + (size_t)a * VD;
+    const float inv = 1.0f / L;
 #pragma unroll
-  for (int i = 0; i < MAX_D / 32; ++i) {
-    const int d = lane + 32 * i;
-    if (d < VD) o[d] = fb_from_float<T>(acc[i] * inv);
+    for (int i = 0; i < NACC; ++i) acc[mm][i] *= inv;
   }
+  T* o = out + (size_t)t * out_stride + (size_t)a * VD;
+  float r = 1.0f;
+  if (MAPS > 1) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      acc[0][i] -= rule.lambda * acc[MAPS - 1][i];
+      if (lane + 32 * i < VD) ss = fmaf(acc[0][i], acc[0][i], ss);
+    }
+    r = rule.post_scale / sqrtf(fb_warp_sum(ss) / (float)VD + rule.post_eps);
+  }
+#pragma unroll
+  for (int i = 0; i < NACC; ++i) {
+    const int d = lane + 32 * i;
+    if (d < VD) o[d] = fb_from_float<T>(acc[0][i] * r);
+  }
+}
+
+// ------------------------------------------- queries with a temperature + cache
+// q_out[t] = q[t] * (1 + coef * ln(floor((p + 1) / every) + 1)) at position p (every 0:
+// the queries as they are); the token's key rows and value rows go into its cache row.
+// qkv: float32 rows [q (nq) | k (G * krow) | v (G * vdim)].
+template <typename T>
+__global__ void q_temp_cache_kernel(const float* qkv, long long ld, T* __restrict__ q_out,
+                                    float coef, int every, const int* __restrict__ positions,
+                                    const int* __restrict__ seq_of_token,
+                                    const int* __restrict__ page_table, int max_pages,
+                                    T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                    long long k_page, long long k_head, long long v_page,
+                                    long long v_head, int nq, int G, int krow, int vdim,
+                                    int write_cache) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int t = blockIdx.x;
+  const int seq = seq_of_token[t];
+  const float* row = qkv + (size_t)t * ld;
+  const int pos = seq < 0 ? 0 : positions[t];
+  const float temp = every > 0 ? 1.0f + coef * logf((float)((pos + 1) / every) + 1.0f) : 1.0f;
+  T* qo = q_out + (size_t)t * nq;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) qo[i] = fb_from_float<T>(__ldcg(row + i) * temp);
+  if (!write_cache || seq < 0) return;
+  const long long page = page_table[(size_t)seq * max_pages + pos / FB_PAGE];
+  const int r = pos % FB_PAGE;
+  const int nk = G * krow, nv = G * vdim;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int g = i / krow, d = i - g * krow;
+    k_cache[page * k_page + g * k_head + (long long)r * krow + d] = fb_from_float<T>(__ldcg(row + nq + i));
+  }
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const int g = i / vdim, d = i - g * vdim;
+    v_cache[page * v_page + g * v_head + (long long)r * vdim + d] =
+        fb_from_float<T>(__ldcg(row + nq + nk + i));
+  }
+}
+
+// --------------------------------------------------- latent rows: norms + rotation
+// The rotation turns neighbouring pairs (2i, 2i + 1) of the first `rot_dims` elements by
+// position * freq[i]; the angle is the float64 product, so it is exact to 32 bits at any position.
+__device__ __forceinline__ void pair_angle(int pos, double freq, float& c, float& s) {
+  double sd, cd;
+  sincos((double)pos * freq, &sd, &cd);
+  c = (float)cd;
+  s = (float)sd;
+}
+
+// in: float32 rows [a (na) | b (nb) | rot (nrot)].
+//   a_out[t] = a / sqrt(mean(a^2) + eps) * wa                      (activation type)
+//   cache row of the token (one key head) = [b / sqrt(mean(b^2) + eps) * wb | rotated rot]
+template <typename T>
+__global__ void latent_rows_kernel(const float* in, long long ld, T* __restrict__ a_out,
+                                   const float* __restrict__ wa, const float* __restrict__ wb,
+                                   float eps, const double* __restrict__ freq, int rot_dims,
+                                   const int* __restrict__ positions,
+                                   const int* __restrict__ seq_of_token,
+                                   const int* __restrict__ page_table, int max_pages,
+                                   T* __restrict__ cache, long long c_page, int na, int nb,
+                                   int nrot, int write_cache) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int seq = seq_of_token[t];
+  const float* row = in + (size_t)t * ld;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < na; i += blockDim.x) {
+    const float v = __ldcg(row + i);
+    sa += v * v;
+  }
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) {
+    const float v = __ldcg(row + na + i);
+    sb += v * v;
+  }
+  sa = fb_block_sum(sa, scratch);
+  sb = fb_block_sum(sb, scratch);
+  const float ra = 1.0f / sqrtf(sa / (float)na + eps);
+  const float rb = 1.0f / sqrtf(sb / (float)nb + eps);
+  for (int i = threadIdx.x; i < na; i += blockDim.x)
+    a_out[(size_t)t * na + i] = fb_from_float<T>(__ldcg(row + i) * ra * wa[i]);
+  if (!write_cache || seq < 0) return;
+  const int pos = positions[t];
+  T* dst = cache + (long long)page_table[(size_t)seq * max_pages + pos / FB_PAGE] * c_page +
+           (long long)(pos % FB_PAGE) * (nb + nrot);
+  for (int i = threadIdx.x; i < nb; i += blockDim.x)
+    dst[i] = fb_from_float<T>(__ldcg(row + na + i) * rb * wb[i]);
+  const float* rot = row + na + nb;
+  for (int i = threadIdx.x; i < nrot / 2 + (nrot & 1); i += blockDim.x) {
+    const float u = __ldcg(rot + 2 * i);
+    if (2 * i + 1 >= nrot) { dst[nb + 2 * i] = fb_from_float<T>(u); continue; }
+    const float v = __ldcg(rot + 2 * i + 1);
+    float c = 1.f, s = 0.f;
+    if (2 * i + 1 < rot_dims) pair_angle(pos, freq[i], c, s);
+    dst[nb + 2 * i] = fb_from_float<T>(u * c - v * s);
+    dst[nb + 2 * i + 1] = fb_from_float<T>(v * c + u * s);
+  }
+}
+
+// q: float32 rows of H heads [plain (d) | rot (c)]. The plain parts go to plain_out
+// [T, H * d]; the rotated parts, turned by the token's position, to wide_out[t, h, off : off + c]
+// with rows of H * wide elements (the query rows of an attention over latent rows, whose
+// first `off` elements a projection of the plain parts fills).
+template <typename T>
+__global__ void split_rotate_kernel(const float* q, long long ld, T* __restrict__ plain_out,
+                                    T* __restrict__ wide_out, int wide, int off,
+                                    const double* __restrict__ freq, int rot_dims,
+                                    const int* __restrict__ positions,
+                                    const int* __restrict__ seq_of_token, int H, int d, int c) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  extern __shared__ float cs[];  // cos, sin of the token's angles: [2][c / 2]
+  const int t = blockIdx.x;
+  const int pos = seq_of_token[t] < 0 ? 0 : positions[t];
+  const int pairs = c / 2;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    float co = 1.f, si = 0.f;
+    if (2 * i + 1 < rot_dims) pair_angle(pos, freq[i], co, si);
+    cs[i] = co;
+    cs[pairs + i] = si;
+  }
+  __syncthreads();
+  const float* row = q + (size_t)t * ld;
+  for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+    const int h = i / d, e = i - h * d;
+    plain_out[(size_t)t * H * d + i] = fb_from_float<T>(__ldcg(row + (size_t)h * (d + c) + e));
+  }
+  for (int i = threadIdx.x; i < H * pairs; i += blockDim.x) {
+    const int h = i / pairs, e = i - h * pairs;
+    const float* src = row + (size_t)h * (d + c) + d + 2 * e;
+    const float u = __ldcg(src), v = __ldcg(src + 1);
+    T* dst = wide_out + ((size_t)t * H + h) * wide + off + 2 * e;
+    dst[0] = fb_from_float<T>(u * cs[e] - v * cs[pairs + e]);
+    dst[1] = fb_from_float<T>(v * cs[e] + u * cs[pairs + e]);
+  }
+  if (c & 1)
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+      wide_out[((size_t)t * H + h) * wide + off + c - 1] =
+          fb_from_float<T>(__ldcg(row + (size_t)h * (d + c) + d + c - 1));
 }
 }  // namespace
 
@@ -307,45 +524,110 @@ FB_API int fb_qk_norm_cache_write(const float* qkv, long long ld, void* q_out, i
   return fb_check_launch("qk_norm_cache_write");
 }
 
+FB_API int fb_q_temp_cache_write(const float* qkv, long long ld, void* q_out, int dtype,
+                                 float coef, int every, const int* positions,
+                                 const int* seq_of_token, const int* page_table, int max_pages,
+                                 void* k_cache, void* v_cache, long long k_page, long long k_head,
+                                 long long v_page, long long v_head, int T, int nq, int G, int krow,
+                                 int vdim, int write_cache, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && nq > 0 && G > 0 && krow > 0 && vdim > 0 && every >= 0,
+             "q_temp_cache_write: bad sizes");
+  FB_REQUIRE(ld >= (long long)nq + (long long)G * (krow + vdim),
+             "q_temp_cache_write: rows of %lld hold no q, k and v", ld);
+  FB_REQUIRE(!write_cache || (k_cache && v_cache && page_table && max_pages > 0),
+             "q_temp_cache_write: no cache to write");
+  if (T == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(q_temp_cache_kernel<E>, dim3(T), dim3(256), 0, stream,
+      qkv, ld, (E*)q_out, coef, every, positions, seq_of_token, page_table, max_pages,
+      (E*)k_cache, (E*)v_cache, k_page, k_head, v_page, v_head, nq, G, krow, vdim, write_cache)));
+  return fb_check_launch("q_temp_cache_write");
+}
+
+FB_API int fb_latent_rows(const float* in, long long ld, void* a_out, int dtype, const float* wa,
+                          const float* wb, float eps, const double* freq, int rot_dims,
+                          const int* positions, const int* seq_of_token, const int* page_table,
+                          int max_pages, void* cache, long long c_page, int T, int na, int nb,
+                          int nrot, int write_cache, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && na > 0 && nb > 0 && nrot >= 0 && rot_dims >= 0 && rot_dims <= nrot &&
+             rot_dims % 2 == 0, "latent_rows: bad sizes");
+  FB_REQUIRE(ld >= (long long)na + nb + nrot, "latent_rows: rows of %lld are too short", ld);
+  FB_REQUIRE(!write_cache || (cache && page_table && max_pages > 0), "latent_rows: no cache to write");
+  if (T == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(latent_rows_kernel<E>, dim3(T), dim3(256), 0, stream, in,
+      ld, (E*)a_out, wa, wb, eps, freq, rot_dims, positions, seq_of_token, page_table, max_pages,
+      (E*)cache, c_page, na, nb, nrot, write_cache)));
+  return fb_check_launch("latent_rows");
+}
+
+FB_API int fb_split_rotate(const float* q, long long ld, void* plain_out, void* wide_out, int dtype,
+                           int wide, int off, const double* freq, int rot_dims,
+                           const int* positions, const int* seq_of_token, int T, int H, int d,
+                           int c, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && H > 0 && d > 0 && c >= 0 && off >= 0 && off + c <= wide &&
+             rot_dims >= 0 && rot_dims <= c && rot_dims % 2 == 0, "split_rotate: bad sizes");
+  FB_REQUIRE(ld >= (long long)H * (d + c), "split_rotate: rows of %lld are too short", ld);
+  if (T == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(split_rotate_kernel<E>, dim3(T), dim3(256),
+      (size_t)(c / 2 * 2 + 2) * 4, stream, q, ld, (E*)plain_out, (E*)wide_out, wide, off, freq,
+      rot_dims, positions, seq_of_token, H, d, c)));
+  return fb_check_launch("split_rotate");
+}
+
 FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long long out_stride,
                              int dtype, const int* positions, const int* seq_of_token,
                              const int* page_table, int max_pages, const void* k_cache,
                              const void* v_cache, long long k_page, long long k_head,
-                             long long v_page, long long v_head, int window, int keep_first,
-                             int sink, float scale, float steep, int T, int H, int G, int D, int VD,
-                             int splits, float* partial, cudaStream_t stream) {
+                             long long v_page, long long v_head, int k_row, int v_row, int window,
+                             int keep_first, int sink, const float* sink_logit, float scale,
+                             float steep, float softcap, int maps, float lambda, float post_eps,
+                             float post_scale, int T, int H, int G, int D, int VD, int splits,
+                             float* partial, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && H > 0 && G > 0 && D > 0 && VD > 0, "attention_sink: bad sizes");
   FB_REQUIRE(H % G == 0, "attention_sink: %d query heads are not a multiple of %d key-value heads",
              H, G);
-  FB_REQUIRE(D <= MAX_D && VD <= MAX_D, "attention_sink: key size %d and value size %d must be "
-             "at most %d", D, VD, MAX_D);
-  const int kvec = D % 8 == 0 && k_page % 8 == 0 && k_head % 8 == 0 && ((uintptr_t)k_cache % 32) == 0;
+  FB_REQUIRE(maps == 1 || maps == 2, "attention_sink: %d maps a head (1 or 2)", maps);
+  FB_REQUIRE(maps * D <= MAX_QD && VD <= (maps == 1 ? 768 : 256),
+             "attention_sink: key size %d x %d maps and value size %d are beyond the kernel's %d "
+             "and %d", D, maps, VD, MAX_QD, maps == 1 ? 768 : 256);
+  FB_REQUIRE(k_row >= maps * D && v_row >= 1, "attention_sink: rows shorter than their vectors");
+  FB_REQUIRE(sink >= 0 && sink <= 2 && (sink != 2 || sink_logit != nullptr),
+             "attention_sink: a sink with a score per head needs the scores");
+  const int kvec = D % 8 == 0 && k_row % 8 == 0 && k_page % 8 == 0 && k_head % 8 == 0 &&
+                   ((uintptr_t)k_cache % 32) == 0;
   FB_REQUIRE(window >= 0 && keep_first >= 0 && max_pages > 0, "attention_sink: bad mask");
   FB_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || partial != nullptr),
              "attention_sink: %d runs need a workspace", splits);
   if (T == 0) return 0;
-  SinkMask mask{window, keep_first, sink ? 1 : 0, scale, steep};
+  ScoreRule rule{window, keep_first, sink, sink_logit, scale, steep, softcap, lambda, post_eps,
+                 post_scale};
   dim3 grid(T, (H + WARPS - 1) / WARPS, splits);
-  const bool vec = VD % 8 == 0 && v_page % 8 == 0 && v_head % 8 == 0 && ((uintptr_t)v_cache % 32) == 0;
+  const bool vec = VD % 8 == 0 && v_row % 8 == 0 && v_page % 8 == 0 && v_head % 8 == 0 &&
+                   ((uintptr_t)v_cache % 32) == 0;
   int lpr = 1;
-  while (lpr * 8 < VD) lpr *= 2;  // lanes that share a value row: a power of two, at most 32
-  if (vec) {
-    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E, true>, dim3(grid),
-        dim3(WARPS * 32), 0, stream, (const E*)q, q_stride, (E*)out, out_stride, positions,
-        seq_of_token, page_table, max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head,
-        v_page, v_head, mask, H, G, D, VD, splits, partial, lpr, kvec)));
-  } else {
-    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E, false>, dim3(grid),
-        dim3(WARPS * 32), 0, stream, (const E*)q, q_stride, (E*)out, out_stride, positions,
-        seq_of_token, page_table, max_pages, (const E*)k_cache, (const E*)v_cache, k_page, k_head,
-        v_page, v_head, mask, H, G, D, VD, splits, partial, lpr, kvec)));
-  }
+  while (lpr * 8 < VD && lpr < 32) lpr *= 2;  // lanes that share a value row: a power of two
+  const size_t smem = (size_t)WARPS * maps * D * 4;
+  const bool wide = VD > 256;
+#define FB_SINK_LAUNCH(VEC_, MAPS_, NACC_)                                                       \
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E, VEC_, MAPS_, NACC_>,          \
+      dim3(grid), dim3(WARPS * 32), smem, stream, (const E*)q, q_stride, (E*)out, out_stride,    \
+      positions, seq_of_token, page_table, max_pages, (const E*)k_cache, (const E*)v_cache,      \
+      k_page, k_head, v_page, v_head, k_row, v_row, rule, H, G, D, VD, splits, partial, lpr,     \
+      kvec)))
+  if (maps == 2) { if (vec) FB_SINK_LAUNCH(true, 2, 8); else FB_SINK_LAUNCH(false, 2, 8); }
+  else if (wide) { if (vec) FB_SINK_LAUNCH(true, 1, 24); else FB_SINK_LAUNCH(false, 1, 24); }
+  else { if (vec) FB_SINK_LAUNCH(true, 1, 8); else FB_SINK_LAUNCH(false, 1, 8); }
+#undef FB_SINK_LAUNCH
   if (splits > 1) {
     int rc = fb_check_launch("attention_sink");
     if (rc) return rc;
-    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_merge_kernel<E>,
-        dim3(T, (H + WARPS - 1) / WARPS), dim3(WARPS * 32), 0, stream, (const float*)partial,
-        (E*)out, out_stride, seq_of_token, H, VD, splits, sink ? 1 : 0)));
+#define FB_MERGE_LAUNCH(MAPS_, NACC_)                                                          \
+    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_merge_kernel<E, MAPS_, NACC_>,      \
+        dim3(T, (H + WARPS - 1) / WARPS), dim3(WARPS * 32), 0, stream, (const float*)partial,  \
+        (E*)out, out_stride, seq_of_token, H, VD, splits, rule)))
+    if (maps == 2) FB_MERGE_LAUNCH(2, 8);
+    else if (wide) FB_MERGE_LAUNCH(1, 24);
+    else FB_MERGE_LAUNCH(1, 8);
+#undef FB_MERGE_LAUNCH
   }
   return fb_check_launch("attention_sink");
 }

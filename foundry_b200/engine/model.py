@@ -187,10 +187,15 @@ class Model:
             values = torch.empty((n, spec.hidden_size), dtype=delta.values.dtype, device=self.device)
             ops.gather_rows(delta.values, ctx.want_rows, values)
             rows_delta, delta = ops.NormedDelta(values, delta.weight, delta.bias, delta.eps), None
+        scale = None
+        if isinstance(delta, ops.ScaledDelta):  # joins the residual times a constant
+            delta, scale = delta.values, delta.scale
         if isinstance(delta, ops.Planes):
-            delta = delta.sum(self.dtype)
+            delta = delta.sum(self.dtype if scale is None else torch.float32)
         if delta is not None:
             rows_delta = torch.empty((n, spec.hidden_size), dtype=delta.dtype, device=self.device)
             ops.gather_rows(delta, ctx.want_rows, rows_delta)
+            if scale is not None:
+                rows_delta = ops.ScaledDelta(rows_delta, scale)
         normed = self.final_norm.add_norm(rows, rows_delta)
         return matmul_nt(normed, self.output_head, logits)

@@ -28,8 +28,8 @@ c_void_p, c_int, c_ll, c_float, c_ull = (ctypes.c_void_p, ctypes.c_int, ctypes.c
 _SIGNATURES = {
     "fb_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "fb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_float, c_void_p, c_int,
-                       c_int, c_int, c_void_p],
-    "fb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                       c_int, c_int, c_float, c_void_p],
+    "fb_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "fb_cast": [c_void_p, c_int, c_void_p, c_int, c_ll, c_void_p],
     "fb_rope_kv_write": [c_void_p, c_int, c_ll, c_int, c_ll, c_void_p, c_int, c_ll, c_void_p,
@@ -37,6 +37,8 @@ _SIGNATURES = {
                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int,
                      c_int, c_void_p],
+    "fb_gemm_simt_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll,
+                             c_int, c_ll, c_ll, c_ll, c_int, c_int, c_void_p],
     "fb_attention_simt": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
                           c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_float, c_void_p],
@@ -95,8 +97,17 @@ _SIGNATURES = {
                                c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_attention_sink": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
                           c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_int,
+                          c_int, c_int, c_void_p, c_float, c_float, c_float, c_int, c_float,
                           c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                           c_void_p],
+    "fb_q_temp_cache_write": [c_void_p, c_ll, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p,
+                              c_void_p, c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int,
+                              c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "fb_latent_rows": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                       c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int,
+                       c_int, c_int, c_int, c_void_p],
+    "fb_split_rotate": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "fb_attention_prefill_masked": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
                                     c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int,
                                     c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p],
@@ -107,10 +118,11 @@ _SIGNATURES = {
     "fb_conv_silu_unit": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_int,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
                           c_int, c_int, c_void_p],
-    "fb_decay_gate": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "fb_decay_gate": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                      c_void_p],
     "fb_state_scan": [c_int, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll,
                       c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
-                      c_int, c_int, c_int, c_int, c_int, c_void_p],
+                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_float, c_void_p,
                           c_int, c_int, c_int, c_int, c_void_p],
     "fb_unary_cast": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -363,6 +375,15 @@ _NO_SCALE = (0, 0, 0, 0, 0.0)
 MAX_SCALE_SHARES = 384  # FB_SKINNY_MAX_SHARES in csrc/gemm_skinny.cu
 
 
+class ScaledDelta:
+    """The output of a part that joins the residual times a constant:
+    resid += scale * values (a tensor or split-K `Planes`). The norm that runs
+    next makes that sum in its own pass (`add_rmsnorm(delta_scale=...)`)."""
+
+    def __init__(self, values, scale: float):
+        self.values, self.scale = values, float(scale)
+
+
 def _scale_of(x):
     """(scale arguments, tensor) of a weight-streaming product's input."""
     if not isinstance(x, RowScaled):
@@ -391,13 +412,15 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> t
 
 # ------------------------------------------------------ residual + RMS norm
 def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
-                out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-    """resid += delta (a tensor, split-K `Planes`, or None), in place, float32;
+                out: Optional[torch.Tensor], delta_scale: float = 1.0) -> Optional[torch.Tensor]:
+    """resid += delta_scale * delta (a tensor, split-K `Planes`, or None), in place, float32;
     out = rmsnorm(resid) * weight. With `out=None` only the sum is made. A
     `NormPending` delta (the sum was made by the projection) comes back as the
     `RowScaled` input of the next projection, and no kernel runs."""
     T, H = resid.shape
     if isinstance(delta, NormPending):
+        if delta_scale != 1.0:
+            raise KernelError("add_rmsnorm: a sum that a projection made cannot be scaled")
         sink = delta.sink
         if sink.resid.data_ptr() != resid.data_ptr() or sink.gamma.data_ptr() != weight.data_ptr() \
                 or sink.eps != float(eps):
@@ -421,18 +444,24 @@ def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
           F32 if delta is None else code_of(delta.dtype), planes, plane_stride,
           _dev(weight, "weight", torch.float32), float(eps),
           0 if out is None else _dev(out, "out"),
-          F32 if out is None else code_of(out.dtype), T, H, _stream())
+          F32 if out is None else code_of(out.dtype), T, H, float(delta_scale), _stream())
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
-    """out[t,i] = silu(gate) * up, with gate i / up i in columns i / I+i, or in
-    columns 2i / 2i+1 when `interleaved`."""
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False,
+             act: str = "silu") -> torch.Tensor:
+    """out[t,i] = act(gate) * up, with gate i / up i in columns i / I+i, or in
+    columns 2i / 2i+1 when `interleaved`; act "silu" or "gelu_tanh". The input may be
+    float32 (a product's unrounded result) where the output is the activation type."""
     T, two_i = gate_up.shape
-    if two_i % 2 or out.shape != (T, two_i // 2) or out.dtype != gate_up.dtype:
+    if two_i % 2 or out.shape != (T, two_i // 2):
         raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} / out {tuple(out.shape)}")
-    _call("fb_silu_mul", _dev(gate_up, "gate_up"), _dev(out, "out"), code_of(out.dtype), T,
-          two_i // 2, 1 if interleaved else 0, _stream())
+    _call("fb_silu_mul", _dev(gate_up, "gate_up"), code_of(gate_up.dtype), _dev(out, "out"),
+          code_of(out.dtype), T, two_i // 2, 1 if interleaved else 0, GLU_ACTIVATIONS[act],
+          _stream())
     return out
 
 
@@ -541,6 +570,32 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
           _rows(out, "out"), code_of(x.dtype), code_of(out.dtype), _stream(),
           tag=("m{} k{} n{}", M, K, N))
     return out
+
+
+def gemm_simt_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[:, b, :] = x[:, b, :] @ w[b]^T for every b, 32-bit FFMA accumulation:
+    x [M, B, K], w [B, N, K], out [M, B, N] (views whose last axis is contiguous; the
+    heads of a per-head projection)."""
+    M, B, K = x.shape
+    N = w.shape[1]
+    if tuple(w.shape) != (B, N, K) or tuple(out.shape) != (M, B, N) or x.dtype != w.dtype:
+        raise KernelError(f"gemm_simt_batched: x {tuple(x.shape)}, w {tuple(w.shape)}, "
+                          f"out {tuple(out.shape)}")
+    for t, name in ((x, "x"), (w, "w"), (out, "out")):
+        if not t.is_cuda or t.stride(2) != 1:
+            raise KernelError(f"{name} must be a CUDA tensor with a contiguous last axis")
+    if M == 0:
+        return out
+    _call("fb_gemm_simt_batched", x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K,
+          x.stride(0), w.stride(1), out.stride(0), B, x.stride(1), w.stride(0), out.stride(1),
+          code_of(x.dtype), code_of(out.dtype), _stream(), tag=("b{} m{} k{} n{}", B, M, K, N))
+    return out
+
+
+def head_products(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """One small product per head: out[:, h, :] = x[:, h, :] @ w[h]^T with x [T, H, K],
+    w [H, N, K], out [T, H, N] (views with a contiguous last axis), accumulated in 32-bit."""
+    return gemm_simt_batched(x, w, out)
 
 
 _SM_OF_DEVICE = {}
@@ -1251,16 +1306,21 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
 
 
 def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor,
-                       then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M, I] = silu(x @ gate^T) * (x @ up^T) with `w_pairs` [2I, K] holding
-    gate i in row 2i and up i in row 2i+1; the activation runs in the product's
-    epilogue, so the [M, 2I] intermediate never reaches memory."""
+                       then_reads: Optional[torch.Tensor] = None, act: str = "silu") -> torch.Tensor:
+    """out[M, I] = act(x @ gate^T) * (x @ up^T) with `w_pairs` [2I, K] holding
+    gate i in row 2i and up i in row 2i+1; with SiLU the activation runs in the
+    product's epilogue, so the [M, 2I] intermediate never reaches memory. Another
+    activation runs behind the product, on its float32 result."""
     M, K = x.shape
     two_i = w_pairs.shape[0]
     if out.shape != (M, two_i // 2) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise KernelError("gemm_bf16_silu_mul: out must be [M, I] bfloat16 with contiguous rows")
     if M == 0:
         return out
+    if act != "silu":
+        tmp = torch.empty((M, two_i), dtype=torch.float32, device=out.device)
+        gemm_bf16(x, w_pairs, tmp)
+        return silu_mul(tmp, out, interleaved=True, act=act)
     usable = _tc_usable(x.values if isinstance(x, RowScaled) else x, w_pairs, out)
     if usable and rows_usable(x, w_pairs):
         return gemm_rows(x, w_pairs, out, silu_mul=True)
@@ -1612,16 +1672,36 @@ SINK_DECODE_WARPS = 2400  # warps a single-token step's attention should come to
 
 def attention_sink(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache, v_cache, H: int,
                    G: int, dim: int, vdim: int, scale: float, window: int = 0, keep_first: int = 0,
-                   sink: bool = False, steep: float = 0.0) -> torch.Tensor:
+                   sink: bool = False, steep: float = 0.0, softcap: float = 0.0,
+                   sink_logits: Optional[torch.Tensor] = None, maps: int = 1,
+                   combine: Optional[tuple] = None, values_in_keys: bool = False) -> torch.Tensor:
     """Causal attention of every token of the step over its sequence's cache,
-    with the mask, bias and sink of csrc/sink_attention.cu. Prompts in bfloat16
-    whose keys and values have one tensor-core head size run the masked form of
-    the tensor-core prompt kernel; everything else the CUDA-core kernel, whose
-    single-token steps cut every token's visible keys into runs."""
+    with the mask, bias, score cap, sink and maps of csrc/sink_attention.cu.
+    `sink_logits` (float32 [H]): the sink's score per head instead of 0. `maps` 2: a
+    query head has two query vectors and a key row two key vectors of `dim` side by
+    side, and `combine` = (lambda, eps, scale) joins the two maps' outputs as
+    (a1 - lambda a2) / rms * scale. `values_in_keys`: the value of a token is the first
+    `vdim` elements of its key row (`v_cache` is not looked at).
+    Prompts in bfloat16 with none of these, whose keys and values have one
+    tensor-core head size, run the masked form of the tensor-core prompt kernel;
+    everything else the CUDA-core kernel, whose single-token steps cut every
+    token's visible keys into runs."""
     T = q.shape[0]
     window, keep_first = int(window or 0), int(keep_first or 0)
-    _check_kv_pair(k_cache, v_cache, G, dim, vdim, q.dtype)
-    if (SINK_ATTENTION_TC and not ctx.is_decode and q.dtype == torch.bfloat16 and dim == vdim
+    k_row = maps * dim
+    if values_in_keys:
+        if vdim > k_row:
+            raise KernelError(f"values of {vdim} do not lie in key rows of {k_row}")
+        v_cache, v_row = k_cache, k_row
+        _check_kv_pair(k_cache, k_cache, G, k_row, k_row, q.dtype)
+    else:
+        v_row = vdim
+        _check_kv_pair(k_cache, v_cache, G, k_row, vdim, q.dtype)
+    if maps not in (1, 2) or (maps == 2) != (combine is not None):
+        raise KernelError("attention_sink: two maps a head need `combine`, one map takes none")
+    plain_rule = softcap == 0.0 and sink_logits is None and maps == 1 and not values_in_keys
+    if (SINK_ATTENTION_TC and plain_rule and not ctx.is_decode and q.dtype == torch.bfloat16
+            and dim == vdim
             and dim in FAST_HEAD_DIMS and H // G <= 16 and k_cache.stride() == v_cache.stride()
             and _tc_attention_ok(q, out)):
         q_blocks = ctx.query_blocks_bound
@@ -1641,18 +1721,86 @@ def attention_sink(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache,
         seen = ctx.max_kv_len if not window else min(ctx.max_kv_len, window + keep_first)
         splits = max(1, min((seen + 63) // 64, SINK_DECODE_WARPS // max(1, T * H), 64))
         if splits > 1:
-            partial = torch.empty(T * H * splits * (vdim + 2), dtype=torch.float32,
+            partial = torch.empty(T * H * splits * maps * (vdim + 2), dtype=torch.float32,
                                   device=q.device).data_ptr()
+    sink_mode = 0
+    if sink_logits is not None:
+        if tuple(sink_logits.shape) != (H,):
+            raise KernelError(f"attention_sink: {tuple(sink_logits.shape)} sink scores for {H} heads")
+        sink_mode = 2
+    elif sink:
+        sink_mode = 1
+    lam, post_eps, post_scale = combine if combine is not None else (0.0, 0.0, 1.0)
     _call("fb_attention_sink", _dev(q, "q", contiguous=False), _rows(q, "q"),
           _dev(out, "out", q.dtype, contiguous=False), _rows(out, "out"), code_of(q.dtype),
           _dev(ctx.positions, "positions", torch.int32),
           _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1],
           k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
-          v_cache.stride(0), v_cache.stride(1), window, keep_first,
-          1 if sink else 0, float(scale), float(steep), T, H, G, dim, vdim, splits, partial,
-          _stream())
+          v_cache.stride(0), v_cache.stride(1), k_row, v_row, window, keep_first, sink_mode,
+          0 if sink_logits is None else _dev(sink_logits, "sink_logits", torch.float32),
+          float(scale), float(steep), float(softcap), maps, float(lam), float(post_eps),
+          float(post_scale), T, H, G, dim, vdim, splits, partial, _stream())
     return out
+
+
+def q_temp_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, coef: float, every: int, positions,
+                       seq_of_token, page_table, k_cache, v_cache, G: int, k_row: int, vdim: int,
+                       write_cache: bool = True) -> torch.Tensor:
+    """Queries times 1 + coef ln(floor((p + 1) / every) + 1) at position p (every 0: as
+    they are) to `q_out`; the token's key rows (G x k_row) and value rows (G x vdim) into
+    its cache row. `qkv`: float32 rows [q | k | v]."""
+    T, nq = q_out.shape
+    kp = vp = 0
+    ks = vs = (0, 0)
+    if write_cache:
+        _check_kv_pair(k_cache, v_cache, G, k_row, vdim, q_out.dtype)
+        kp, vp = k_cache.data_ptr(), v_cache.data_ptr()
+        ks, vs = (k_cache.stride(0), k_cache.stride(1)), (v_cache.stride(0), v_cache.stride(1))
+    _call("fb_q_temp_cache_write", _dev(qkv, "qkv", torch.float32, contiguous=False),
+          _rows(qkv, "qkv"), _dev(q_out, "q_out"), code_of(q_out.dtype), float(coef), int(every),
+          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1], kp, vp, *ks, *vs,
+          T, nq, G, k_row, vdim, 1 if write_cache else 0, _stream())
+    return q_out
+
+
+def latent_rows(x: torch.Tensor, a_out: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor,
+                eps: float, freq: torch.Tensor, rot_dims: int, positions, seq_of_token, page_table,
+                cache: torch.Tensor, nb: int, nrot: int, write_cache: bool = True) -> torch.Tensor:
+    """x: float32 rows [a | b (nb) | rot (nrot)]. a_out = rmsnorm(a) * wa; the token's
+    cache row ([pages, 1, PAGE, nb + nrot]) = [rmsnorm(b) * wb | rot with its first
+    `rot_dims` elements turned in neighbouring pairs by position * freq]."""
+    T, na = a_out.shape
+    if write_cache:
+        _check_kv_pair(cache, cache, 1, nb + nrot, nb + nrot, a_out.dtype)
+    if freq.dtype != torch.float64 or freq.numel() * 2 < rot_dims:
+        raise KernelError("latent_rows: frequencies are float64, one for every pair")
+    _call("fb_latent_rows", _dev(x, "x", torch.float32, contiguous=False), _rows(x, "x"),
+          _dev(a_out, "a_out"), code_of(a_out.dtype), _dev(wa, "wa", torch.float32),
+          _dev(wb, "wb", torch.float32), float(eps), _dev(freq, "freq", torch.float64), rot_dims,
+          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1],
+          cache.data_ptr() if write_cache else 0, cache.stride(0) if write_cache else 0, T, na, nb,
+          nrot, 1 if write_cache else 0, _stream())
+    return a_out
+
+
+def split_rotate(q: torch.Tensor, plain_out: torch.Tensor, wide_out: torch.Tensor, offset: int,
+                 freq: torch.Tensor, rot_dims: int, positions, seq_of_token, H: int, d: int,
+                 c: int) -> None:
+    """q: float32 rows of H heads [plain (d) | rot (c)]. plain_out [T, H * d] takes the
+    plain parts; wide_out [T, H, wide] takes the rotated parts at [offset, offset + c)."""
+    T = q.shape[0]
+    wide = wide_out.shape[2]
+    if tuple(plain_out.shape) != (T, H * d) or tuple(wide_out.shape[:2]) != (T, H) \
+            or plain_out.dtype != wide_out.dtype or freq.dtype != torch.float64:
+        raise KernelError("split_rotate: shapes differ")
+    _call("fb_split_rotate", _dev(q, "q", torch.float32, contiguous=False), _rows(q, "q"),
+          _dev(plain_out, "plain_out"), _dev(wide_out, "wide_out"), code_of(plain_out.dtype), wide,
+          offset, _dev(freq, "freq", torch.float64), rot_dims,
+          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+          T, H, d, c, _stream())
 
 
 # ---------------------------------------------------- mixers with a carried state
@@ -1721,25 +1869,31 @@ def conv_silu_unit(ctx, x: torch.Tensor, weight: torch.Tensor, state: StateRows,
     return bool(ctx.is_decode)
 
 
-def decay_gate(x: torch.Tensor, per_head: int, bias: torch.Tensor, A: Optional[torch.Tensor]):
-    """In place on float32 [T, n]: with `A` ([heads]) exp(-exp(A) softplus(x + bias)),
-    without it exp(-exp(x + bias))."""
+def decay_gate(x: torch.Tensor, per_head: int, bias: torch.Tensor, A: Optional[torch.Tensor],
+               out: Optional[torch.Tensor] = None):
+    """On float32 rows [T, n] (in place, or from a strided view `x` into the contiguous
+    `out`): with `A` ([heads]) exp(-exp(A) softplus(x + bias)), one decay for every
+    `per_head` channels' head (per_head 1: one a head); without it exp(-exp(x + bias))."""
     T, n = x.shape
-    if bias.numel() != n:
+    out = x if out is None else out
+    if bias.numel() != n or tuple(out.shape) != (T, n):
         raise KernelError("decay_gate: the bias does not fit the rows")
-    _call("fb_decay_gate", _dev(x, "x", torch.float32), T, n, per_head,
+    _call("fb_decay_gate", _dev(x, "x", torch.float32, contiguous=False), _rows(x, "x"),
+          _dev(out, "out", torch.float32), T, n, per_head,
           0 if A is None else _dev(A, "A", torch.float32), _dev(bias, "bias", torch.float32),
           1 if A is None else 0, _stream())
-    return x
+    return out
 
 
 SCAN_DELTA, SCAN_WKV = 0, 1
 
 
 def state_scan(ctx, mode: int, q, k, v, g, state: StateRows, field: str, out: torch.Tensor,
-               H: int, rep: int, dim: int, vdim: int, beta=None, bonus=None) -> torch.Tensor:
+               H: int, rep: int, dim: int, vdim: int, beta=None, bonus=None,
+               decay_per_head: bool = False) -> torch.Tensor:
     """The recurrence of csrc/sequence_mix.cu over every sequence of the step.
-    q, k: float32 views [T, >= (H / rep) * dim]; v [T, >= H * vdim]; g [T, H * dim];
+    q, k: float32 views [T, >= (H / rep) * dim]; v [T, >= H * vdim]; g [T, H * dim], or
+    [T, H] with `decay_per_head` (one decay for all key channels of a head);
     beta (delta) a float32 view [T, >= H]; bonus (wkv) [H, dim]; out float32 [T, H * vdim]."""
     T = out.shape[0]
     if out.shape != (T, H * vdim) or out.dtype != torch.float32 or not out.is_contiguous():
@@ -1753,7 +1907,8 @@ def state_scan(ctx, mode: int, q, k, v, g, state: StateRows, field: str, out: to
           0 if beta is None else _rows(beta, "beta"),
           0 if bonus is None else _dev(bonus, "bonus", f32), state.rows.data_ptr(), state.stride,
           state.offset[field], out.data_ptr(), _dev(ctx.cu_tokens, "cu_tokens", torch.int32),
-          _dev(ctx.slots, "slots", torch.int32), ctx.n_seqs, H, rep, dim, vdim, _stream())
+          _dev(ctx.slots, "slots", torch.int32), ctx.n_seqs, H, rep, dim, vdim,
+          1 if decay_per_head else 0, _stream())
     return out
 
 

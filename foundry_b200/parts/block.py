@@ -164,3 +164,71 @@ def _as_rows(y):
     """A part's output as one tensor (split-K planes are summed in 32-bit)."""
     from ..kernels import ops
     return y.sum(torch.float32) if isinstance(y, ops.Planes) else y
+
+
+@register_block("scaled_pre_norm_residual")
+class ScaledPreNormBlock(Part):
+    """The pre-norm arrangement with a constant on every part's output:
+
+        x <- x + m * mixer(norm1(x));  x <- x + m * feed_forward(norm2(x))
+
+    the second line only where the layer has a feed-forward. The products are
+    not scaled: a part's output leaves as an `ops.ScaledDelta` and the norm
+    that runs next makes `x += m * y` in 32-bit in its own pass over the row."""
+    replay_safe = True
+
+    def __init__(self, layer: LayerSpec, residual_scale: float = 1.0, *, dtype: torch.dtype,
+                 device: torch.device):
+        ctx = dict(dtype=dtype, device=device)
+        self.prefix = layer.prefix
+        self.names = dict(layer.names)
+        self.residual_scale = float(residual_scale)
+        self.mixer = MIXERS.build(layer.mixer, **ctx)
+        self.mixer_norm = NORMS.build(layer.mixer_norm, **ctx)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            if layer.feed_forward_norm is None:
+                raise ValueError("scaled_pre_norm_residual: a feed-forward needs its norm")
+            self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, **ctx)
+            self.feed_forward_norm = NORMS.build(layer.feed_forward_norm, **ctx)
+
+    def _named(self):
+        p, n = self.prefix, self.names
+        named = [(self.mixer_norm, f"{p}.{n['mixer_norm']}"), (self.mixer, f"{p}.{n['mixer']}")]
+        if self.feed_forward is not None:
+            named += [(self.feed_forward_norm, f"{p}.{n['feed_forward_norm']}"),
+                      (self.feed_forward, f"{p}.{n['feed_forward']}")]
+        return named
+
+    def parts(self):
+        return [part for part, _ in self._named()]
+
+    def expected_tensors(self, prefix: str = "") -> Dict[str, ExpectedTensor]:
+        out: Dict[str, ExpectedTensor] = {}
+        for part, name in self._named():
+            out.update(part.expected_tensors(name))
+        return out
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        for part, name in self._named():
+            part.load(name, fetch)
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def first_weight(self):
+        return first_weight_of(self.mixer)
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache):
+        from ..kernels import ops
+        after_block = getattr(ctx, "reads_after_part", None)
+        ctx.residual_sink = None  # a projection's own sum would miss the constant
+        normed = self.mixer_norm.add_norm(resid, delta)
+        ctx.reads_after_part = (first_weight_of(self.feed_forward) if self.feed_forward is not None
+                                else after_block)
+        mixed = ops.ScaledDelta(self.mixer.forward(ctx, normed, cache), self.residual_scale)
+        if self.feed_forward is None:
+            return mixed
+        normed = self.feed_forward_norm.add_norm(resid, mixed)
+        ctx.reads_after_part = after_block
+        return ops.ScaledDelta(self.feed_forward.forward(ctx, normed), self.residual_scale)

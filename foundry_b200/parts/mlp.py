@@ -1,6 +1,8 @@
-"""SwiGLU feed-forward: down(silu(gate(x)) * up(x)), no biases
-(src/models/llama/mlp.rs:49-58); SiLU is x / (1 + exp(-x)) in 32-bit
-(src/nn/activation.rs:18-27). gate and up are one fused product.
+"""Gated feed-forward: down(act(gate(x)) * up(x)), no biases. With act = SiLU
+it is the reference's SwiGLU (src/models/llama/mlp.rs:49-58; SiLU is
+x / (1 + exp(-x)) in 32-bit, src/nn/activation.rs:18-27); `activation =
+"gelu_tanh"` makes it 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+gate and up are one fused product.
 """
 from __future__ import annotations
 
@@ -21,7 +23,10 @@ class SwiGLU(Part):
 
     def __init__(self, hidden_size: int, intermediate_size: int, *, dtype: torch.dtype,
                  device: torch.device, names=("gate_proj", "up_proj", "down_proj"),
-                 suffix: str = ".weight"):
+                 suffix: str = ".weight", activation: str = "silu"):
+        if activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r}; known: {sorted(ops.GLU_ACTIVATIONS)}")
+        self.activation = activation
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.dtype, self.device = dtype, device
         self.names, self.suffix = tuple(names), suffix  # the three projections in the files
@@ -52,9 +57,10 @@ class SwiGLU(Part):
         hidden = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         if x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16:
             ops.gemm_bf16_silu_mul(x, self.gate_up, hidden,  # activation in the epilogue
-                                   then_reads=self.down.weight)
+                                   then_reads=self.down.weight, act=self.activation)
         else:
-            ops.silu_mul(matmul_nt(ops.plain(x), self.gate_up), hidden, interleaved=True)
+            ops.silu_mul(matmul_nt(ops.plain(x), self.gate_up), hidden, interleaved=True,
+                         act=self.activation)
         return self.down.forward(hidden, allow_planes=True,
                                  then_reads=getattr(ctx, "reads_after_part", None),
                                  residual=getattr(ctx, "residual_sink", None))

@@ -21,16 +21,18 @@ from .base import Fetch, Part, register_norm
 class RMSNorm(Part):
     replay_safe = True  # forward reads nothing of the step on the host
 
-    def __init__(self, size: int, eps: float, *, dtype: torch.dtype, device: torch.device):
+    def __init__(self, size: int, eps: float, weight_suffix: str = ".weight", *,
+                 dtype: torch.dtype, device: torch.device):
         self.size, self.eps = size, float(eps)
+        self.weight_suffix = weight_suffix  # the tensor is `<prefix><weight_suffix>`
         self.dtype, self.device = dtype, device
         self.weight: Optional[torch.Tensor] = None
 
     def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
-        return {f"{prefix}.weight": ExpectedTensor((self.size,))}
+        return {f"{prefix}{self.weight_suffix}": ExpectedTensor((self.size,))}
 
     def load(self, prefix: str, fetch: Fetch) -> None:
-        self.weight = fetch(f"{prefix}.weight").to(torch.float32).contiguous()
+        self.weight = fetch(f"{prefix}{self.weight_suffix}").to(torch.float32).contiguous()
 
     def sink(self, resid: torch.Tensor) -> Optional[ops.ResidualSink]:
         """What the projection in front of this norm needs to make the sum and
@@ -40,14 +42,17 @@ class RMSNorm(Part):
         return ops.ResidualSink(resid, self.weight, self.eps)
 
     def add_norm(self, resid: torch.Tensor, delta, out: Optional[torch.Tensor] = None):
-        """resid += delta (a tensor, split-K `ops.Planes`, or None); returns
+        """resid += delta (a tensor, split-K `ops.Planes`, an `ops.ScaledDelta`, or None); returns
         norm(resid) in the activation dtype. A delta that a projection made
         with this norm's `sink` comes back as an `ops.RowScaled`."""
         if isinstance(delta, ops.NormPending):
             return ops.add_rmsnorm(resid, delta, self.weight, self.eps, None)
         if out is None:
             out = torch.empty(resid.shape, dtype=self.dtype, device=resid.device)
-        return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
+        scale = 1.0
+        if isinstance(delta, ops.ScaledDelta):  # resid += scale * values
+            delta, scale = delta.values, delta.scale
+        return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, delta_scale=scale)
 
 
 @register_norm("layer_norm")

@@ -12,6 +12,13 @@
     S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
     out = Wo [ o / rms(o) * norm * sigmoid(Wg2 (Wg1 h)) ]   (norm [vdim], shared by heads)
 
+`gated_delta`: the same rule with ONE decay per head and full-rank gates.
+
+    q, k, v, convolutions, SiLU and unit vectors as above;  beta = sigmoid(Wb h);
+    g = exp(-exp(A_log[a]) softplus(Wa h + dt_bias))  one number per head (Wa [heads, W]);
+    S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+    out = Wo [ o / rms(o) * norm * silu(Wg h) ]      (Wg [heads * vdim, W])
+
 `wkv_time_mix`: RWKV-style time mixing.
 
     with h' the previous token's h (zeros at the start): m_s = h + (h' - h) mu_s for
@@ -106,6 +113,73 @@ class GatedDeltaChannel(Part):
                        "S", o, H, H // G, d, v, beta=p[:, C:])
         y = torch.empty((T, H * v), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, self.norm, False, gate, "sigmoid", self.eps, y, H, v)
+        return product_f32(y, self.o)
+
+
+@register_mixer("gated_delta")
+class GatedDelta(Part):
+    """The gated delta rule with a decay per head (see the module's notes). The
+    output gate's activation and the constant inside the unit vectors' root are
+    parameters."""
+    replay_safe = True
+
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int,
+                 eps: float, unit_eps: float = 1e-6, gate: str = "silu", *,
+                 dtype: torch.dtype, device: torch.device):
+        if kv_heads <= 0 or heads % kv_heads:
+            raise ValueError(f"{heads} heads are not a multiple of {kv_heads} key heads")
+        if dim > 512:
+            raise ValueError(f"{dim} key channels a head: the recurrence kernel holds at most 512")
+        if gate not in ("silu", "sigmoid"):
+            raise ValueError(f"output gate {gate!r}; known: silu, sigmoid")
+        self.width, self.heads, self.kv_heads, self.dim, self.vdim = width, heads, kv_heads, dim, vdim
+        self.taps, self.eps, self.unit_eps, self.gate = int(taps), float(eps), float(unit_eps), gate
+        self.dtype, self.device = dtype, device
+        self.channels = 2 * kv_heads * dim + heads * vdim
+        self.fields = [("tail", (self.taps - 1) * self.channels), ("S", heads * dim * vdim)]
+
+    def _shapes(self):
+        W, H, G, d, v = self.width, self.heads, self.kv_heads, self.dim, self.vdim
+        return {"q": (G * d, W), "q.conv": (G * d, self.taps), "k": (G * d, W),
+                "k.conv": (G * d, self.taps), "v": (H * v, W), "v.conv": (H * v, self.taps),
+                "b": (H, W), "A_log": (H,), "norm": (v,), "a": (H, W), "dt_bias": (H,),
+                "g": (H * v, W), "o": (W, H * v)}
+
+    def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
+        return {f"{prefix}.{n}": ExpectedTensor(s) for n, s in self._shapes().items()}
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        f = lambda n: fetch(f"{prefix}.{n}")
+        # every projection of h in one product: q | k | v | gate | beta | decay
+        self.w_in = torch.cat([f("q"), f("k"), f("v"), f("g"), f("b"), f("a")], 0).contiguous()
+        self.conv = _f32(torch.cat([f("q.conv"), f("k.conv"), f("v.conv")], 0))
+        self.o = f("o").contiguous()
+        self.A_log, self.dt_bias, self.norm = _f32(f("A_log")), _f32(f("dt_bias")), _f32(f("norm"))
+
+    def cache_request(self) -> StateRequest:
+        return StateRequest((sum(n for _, n in self.fields),), torch.float32)
+
+    def first_weight(self):
+        return self.w_in
+
+    def forward(self, ctx, x, cache: StateView):
+        T = x.shape[0]
+        H, G, d, v, C = self.heads, self.kv_heads, self.dim, self.vdim, self.channels
+        f32 = dict(dtype=torch.float32, device=x.device)
+        state = ops.StateRows(cache.rows, self.fields)
+        p = product_f32(x, self.w_in)  # [T, C | H v | H | H]
+        qkv = torch.empty((T, C), **f32)
+        if not ops.conv_silu_unit(ctx, p, self.conv, state, "tail", qkv, C, n_unit=2 * G, dim=d,
+                                  n_scaled=G, extra=d ** -0.5, unit_eps=self.unit_eps):
+            ops.state_tail_update(ctx, p, state, "tail", self.taps - 1, C)
+        at = C + H * v
+        decay = torch.empty((T, H), **f32)
+        ops.decay_gate(p[:, at + H:at + 2 * H], 1, self.dt_bias, self.A_log, out=decay)
+        o = torch.empty((T, H * v), **f32)
+        ops.state_scan(ctx, ops.SCAN_DELTA, qkv, qkv[:, G * d:], qkv[:, 2 * G * d:], decay, state,
+                       "S", o, H, H // G, d, v, beta=p[:, at:at + H], decay_per_head=True)
+        y = torch.empty((T, H * v), dtype=x.dtype, device=x.device)
+        ops.head_norm_gate(o, self.norm, False, p[:, C:at], self.gate, self.eps, y, H, v)
         return product_f32(y, self.o)
 
 
