@@ -336,8 +336,9 @@ def design_point(preset_name: str, batch: int, context: int, prompt_tokens: int,
 
 
 def run_design(args) -> dict:
-    """`--design rupotar`: Rupotar stacks of real layer sizes beside Llama stacks of
-    the same width, heads, feed-forward width, depth and vocabulary."""
+    """`--design NAME`: stacks of that design at real layer sizes beside Llama stacks of
+    the same width, heads, feed-forward width, depth and vocabulary (and, for a design
+    with recurrent mixers of its own, beside Rupotar's as well: `--beside`)."""
     hbm_gbs, tflops_burst, _, source = peaks()
     out = {"design": args.design, "dtype": "bf16", "n_gpus": 1,
            "data": "synthetic: random token ids (SplitMix64), random-init weights",
@@ -348,7 +349,7 @@ def run_design(args) -> dict:
         out["sizes"][size] = {
             name: design_point(f"{name}-{size}", args.batch, args.design_context, PREFILL_TOKENS,
                                max(8, args.steps // 4), args.warmup)
-            for name in (args.design, "llama")}
+            for name in dict.fromkeys([args.design] + args.beside.split(","))}
     out["clocks"] = sampler.stop()
     return out
 
@@ -498,7 +499,9 @@ def main() -> int:
                         help="leave out the 1B and 8B workload points")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch decode kernels one by one (for profilers)")
-    parser.add_argument("--design", default=None, choices=["rupotar"],
+    parser.add_argument("--beside", default="llama",
+                        help="with --design: the designs to time beside it, with commas between them")
+    parser.add_argument("--design", default=None, choices=["rupotar", "vonulorn"],
                         help="instead of the default workload: stacks of this design at real layer "
                              "sizes beside Llama stacks of equal size (prefill and decode "
                              "throughput, per-kernel device times)")

@@ -44,7 +44,33 @@ def _rupotar(layers, width, heads, kv_heads, dim, ff, vocab, window=1024, keep_f
             "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": stack, "loop": loop}
 
 
+def _vonulorn(layers, width, heads, kv_heads, dim, ff, vocab, kv_rank, q_rank, taps=4) -> Dict:
+    """A Vonulorn stack of real layer sizes: the three mixers in turn (delta,
+    differential attention, latent attention), every layer with a dense
+    feed-forward. The differential attention has half the heads with two maps of
+    `dim` each and values of 2 dim, so its scores and sums cost what `heads` plain
+    heads of `dim` cost; the latent attention rotates half a head's size beside it."""
+    stack = []
+    for i in range(layers):
+        kind = ("delta", "attention", "latent_attention")[i % 3]
+        if kind == "delta":
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": taps}
+        elif kind == "attention":
+            mixer = {"heads": heads // 2, "kv_heads": max(1, kv_heads // 2), "dim": dim,
+                     "vdim": 2 * dim, "scale": dim ** -0.5, "softcap": 30.0, "diff": 0.6,
+                     "q_temp": {"coef": 0.3, "every": 64}}
+        else:
+            mixer = {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim,
+                     "kv_rank": kv_rank, "q_rank": q_rank, "scale": (dim + dim // 2) ** -0.5,
+                     "rot": {"base": 1000000.0, "dims": dim // 2}}
+        stack.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Vonulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "layers": stack}
+
+
 PRESETS: Dict[str, Dict] = {
+    "vonulorn-1b-layers": _vonulorn(6, 2048, 32, 8, 64, 8192, 32000, 256, 768),
+    "vonulorn-3b-layers": _vonulorn(6, 3072, 24, 8, 128, 8192, 32000, 512, 1536),
     # six layers of the 1B and 3B layer sizes, as Rupotar and as Llama, for side-by-side timing
     "rupotar-1b-layers": _rupotar(6, 2048, 32, 8, 64, 8192, 32000),
     "rupotar-3b-layers": _rupotar(6, 3072, 24, 8, 128, 8192, 32000),
