@@ -48,7 +48,7 @@ def _vonulorn(layers, width, heads, kv_heads, dim, ff, vocab, kv_rank, q_rank, t
     """A Vonulorn stack of real layer sizes: the three mixers in turn (delta,
     differential attention, latent attention), every layer with a dense
     feed-forward. The differential attention has half the heads with two maps of
-    `dim` each and values of 2 dim, so its scores and sums cost what `heads` plain
+    at most 64 each and values twice that, so its scores and sums cost what `heads` plain
     heads of `dim` cost; the latent attention rotates half a head's size beside it."""
     stack = []
     for i in range(layers):
@@ -56,9 +56,10 @@ def _vonulorn(layers, width, heads, kv_heads, dim, ff, vocab, kv_rank, q_rank, t
         if kind == "delta":
             mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": taps}
         elif kind == "attention":
-            mixer = {"heads": heads // 2, "kv_heads": max(1, kv_heads // 2), "dim": dim,
-                     "vdim": 2 * dim, "scale": dim ** -0.5, "softcap": 30.0, "diff": 0.6,
-                     "q_temp": {"coef": 0.3, "every": 64}}
+            each = min(dim, 64)  # a map's key size; as many heads as keep the projections' sizes
+            mixer = {"heads": heads * dim // (2 * each), "kv_heads": max(1, kv_heads * dim // (2 * each)),
+                     "dim": each, "vdim": 2 * each, "scale": each ** -0.5, "softcap": 30.0,
+                     "diff": 0.6, "q_temp": {"coef": 0.3, "every": 64}}
         else:
             mixer = {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim,
                      "kv_rank": kv_rank, "q_rank": q_rank, "scale": (dim + dim // 2) ** -0.5,

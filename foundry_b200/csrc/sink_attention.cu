@@ -421,8 +421,8 @@ __global__ void latent_rows_kernel(const float* in, long long ld, T* __restrict_
                                    const int* __restrict__ positions,
                                    const int* __restrict__ seq_of_token,
                                    const int* __restrict__ page_table, int max_pages,
-                                   T* __restrict__ cache, long long c_page, int na, int nb,
-                                   int nrot, int write_cache) {
+                                   T* __restrict__ cache, long long c_page, T* __restrict__ b_out,
+                                   int na, int nb, int nrot, int write_cache) {
   fb_pdl_launch();
   fb_pdl_wait();
   __shared__ float scratch[32];
@@ -444,26 +444,36 @@ __global__ void latent_rows_kernel(const float* in, long long ld, T* __restrict_
   const float rb = 1.0f / sqrtf(sb / (float)nb + eps);
   for (int i = threadIdx.x; i < na; i += blockDim.x)
     a_out[(size_t)t * na + i] = fb_from_float<T>(__ldcg(row + i) * ra * wa[i]);
-  if (!write_cache || seq < 0) return;
-  const int pos = positions[t];
-  T* dst = cache + (long long)page_table[(size_t)seq * max_pages + pos / FB_PAGE] * c_page +
-           (long long)(pos % FB_PAGE) * (nb + nrot);
-  for (int i = threadIdx.x; i < nb; i += blockDim.x)
-    dst[i] = fb_from_float<T>(__ldcg(row + na + i) * rb * wb[i]);
+  // the same row goes to the token's place in the cache and, where asked for, to row t
+  // of a buffer of the step (for a consumer that works on the step's own rows)
+  const bool to_cache = write_cache && seq >= 0;
+  if (!to_cache && b_out == nullptr) return;
+  const int pos = seq < 0 ? 0 : positions[t];
+  T* dst = !to_cache ? nullptr
+      : cache + (long long)page_table[(size_t)seq * max_pages + pos / FB_PAGE] * c_page +
+            (long long)(pos % FB_PAGE) * (nb + nrot);
+  T* copy = b_out == nullptr ? nullptr : b_out + (size_t)t * (nb + nrot);
+  auto put = [&](int i, float v) {
+    const T e = fb_from_float<T>(v);
+    if (dst != nullptr) dst[i] = e;
+    if (copy != nullptr) copy[i] = e;
+  };
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) put(i, __ldcg(row + na + i) * rb * wb[i]);
   const float* rot = row + na + nb;
   for (int i = threadIdx.x; i < nrot / 2 + (nrot & 1); i += blockDim.x) {
     const float u = __ldcg(rot + 2 * i);
-    if (2 * i + 1 >= nrot) { dst[nb + 2 * i] = fb_from_float<T>(u); continue; }
+    if (2 * i + 1 >= nrot) { put(nb + 2 * i, u); continue; }
     const float v = __ldcg(rot + 2 * i + 1);
     float c = 1.f, s = 0.f;
     if (2 * i + 1 < rot_dims) pair_angle(pos, freq[i], c, s);
-    dst[nb + 2 * i] = fb_from_float<T>(u * c - v * s);
-    dst[nb + 2 * i + 1] = fb_from_float<T>(v * c + u * s);
+    put(nb + 2 * i, u * c - v * s);
+    put(nb + 2 * i + 1, v * c + u * s);
   }
 }
 
 // q: float32 rows of H heads [plain (d) | rot (c)]. The plain parts go to plain_out
-// [T, H * d]; the rotated parts, turned by the token's position, to wide_out[t, h, off : off + c]
+// [T, H * d] (or, with `plain_into_wide`, to the first d elements of the head's wide row,
+// which then is the whole rotated query head); the rotated parts, turned by the token's position, to wide_out[t, h, off : off + c]
 // with rows of H * wide elements (the query rows of an attention over latent rows, whose
 // first `off` elements a projection of the plain parts fills).
 template <typename T>
@@ -471,7 +481,8 @@ __global__ void split_rotate_kernel(const float* q, long long ld, T* __restrict_
                                     T* __restrict__ wide_out, int wide, int off,
                                     const double* __restrict__ freq, int rot_dims,
                                     const int* __restrict__ positions,
-                                    const int* __restrict__ seq_of_token, int H, int d, int c) {
+                                    const int* __restrict__ seq_of_token, int H, int d, int c,
+                                    int plain_into_wide) {
   fb_pdl_launch();
   fb_pdl_wait();
   extern __shared__ float cs[];  // cos, sin of the token's angles: [2][c / 2]
@@ -488,7 +499,9 @@ __global__ void split_rotate_kernel(const float* q, long long ld, T* __restrict_
   const float* row = q + (size_t)t * ld;
   for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
     const int h = i / d, e = i - h * d;
-    plain_out[(size_t)t * H * d + i] = fb_from_float<T>(__ldcg(row + (size_t)h * (d + c) + e));
+    const T v = fb_from_float<T>(__ldcg(row + (size_t)h * (d + c) + e));
+    if (plain_into_wide) wide_out[((size_t)t * H + h) * wide + e] = v;  // (off == d then)
+    else plain_out[(size_t)t * H * d + i] = v;
   }
   for (int i = threadIdx.x; i < H * pairs; i += blockDim.x) {
     const int h = i / pairs, e = i - h * pairs;
@@ -546,8 +559,8 @@ FB_API int fb_q_temp_cache_write(const float* qkv, long long ld, void* q_out, in
 FB_API int fb_latent_rows(const float* in, long long ld, void* a_out, int dtype, const float* wa,
                           const float* wb, float eps, const double* freq, int rot_dims,
                           const int* positions, const int* seq_of_token, const int* page_table,
-                          int max_pages, void* cache, long long c_page, int T, int na, int nb,
-                          int nrot, int write_cache, cudaStream_t stream) {
+                          int max_pages, void* cache, long long c_page, void* b_out, int T, int na,
+                          int nb, int nrot, int write_cache, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && na > 0 && nb > 0 && nrot >= 0 && rot_dims >= 0 && rot_dims <= nrot &&
              rot_dims % 2 == 0, "latent_rows: bad sizes");
   FB_REQUIRE(ld >= (long long)na + nb + nrot, "latent_rows: rows of %lld are too short", ld);
@@ -555,21 +568,23 @@ FB_API int fb_latent_rows(const float* in, long long ld, void* a_out, int dtype,
   if (T == 0) return 0;
   FB_DISPATCH_DTYPE(dtype, E, (fb_launch(latent_rows_kernel<E>, dim3(T), dim3(256), 0, stream, in,
       ld, (E*)a_out, wa, wb, eps, freq, rot_dims, positions, seq_of_token, page_table, max_pages,
-      (E*)cache, c_page, na, nb, nrot, write_cache)));
+      (E*)cache, c_page, (E*)b_out, na, nb, nrot, write_cache)));
   return fb_check_launch("latent_rows");
 }
 
 FB_API int fb_split_rotate(const float* q, long long ld, void* plain_out, void* wide_out, int dtype,
                            int wide, int off, const double* freq, int rot_dims,
                            const int* positions, const int* seq_of_token, int T, int H, int d,
-                           int c, cudaStream_t stream) {
+                           int c, int plain_into_wide, cudaStream_t stream) {
+  FB_REQUIRE(plain_into_wide ? off == d : plain_out != nullptr,
+             "split_rotate: the plain parts have no place");
   FB_REQUIRE(T >= 0 && H > 0 && d > 0 && c >= 0 && off >= 0 && off + c <= wide &&
              rot_dims >= 0 && rot_dims <= c && rot_dims % 2 == 0, "split_rotate: bad sizes");
   FB_REQUIRE(ld >= (long long)H * (d + c), "split_rotate: rows of %lld are too short", ld);
   if (T == 0) return 0;
   FB_DISPATCH_DTYPE(dtype, E, (fb_launch(split_rotate_kernel<E>, dim3(T), dim3(256),
       (size_t)(c / 2 * 2 + 2) * 4, stream, q, ld, (E*)plain_out, (E*)wide_out, wide, off, freq,
-      rot_dims, positions, seq_of_token, H, d, c)));
+      rot_dims, positions, seq_of_token, H, d, c, plain_into_wide)));
   return fb_check_launch("split_rotate");
 }
 

@@ -55,6 +55,10 @@ class StepContext:
     # ... and whether some sequence brings 64 tokens or more (the choice between
     # the two prompt-attention kernels, made as a plain step makes it)
     long_queries: bool = False
+    # Every sequence of the step begins at its first token, so all keys it can see are
+    # the step's own rows (a mixer may then work on those rows instead of the cache);
+    # in a replayed step it is fixed when the step is captured
+    fresh: bool = False
     _tables: Dict[int, torch.Tensor] = field(default_factory=dict)
     # The weight that the step streams after the part being run (a prefetch
     # hint, set by the model and the blocks as they go; None = unknown).
@@ -181,7 +185,8 @@ def build_context(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_siz
         slots=part[4], cu_tokens=part[5], kv_lens=part[6],
         slots_host=plan.slots, cu_tokens_host=plan.cu, kv_lens_host=plan.kv_lens,
         is_decode=all(n == 1 for n in lens), max_q_len=max(lens), max_kv_len=max(plan.kv_lens),
-        unequal_lengths=lengths_are_unequal(plan.kv_lens))
+        unequal_lengths=lengths_are_unequal(plan.kv_lens),
+        fresh=all(plan.kv_lens[i] == lens[i] for i in range(n_seqs)))
     for i, (group, width, _) in enumerate(plan.tables):
         ctx._tables[id(group)] = part[7 + i].view(n_seqs, width)
     return ctx

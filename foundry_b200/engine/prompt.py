@@ -51,9 +51,10 @@ def token_bucket(n: int) -> int:
 class PromptRunner:
     """Fixed buffers and the captured graph of one bucket."""
 
-    def __init__(self, engine, tokens: int, seqs: int, width: int, want: int, long_queries: bool):
+    def __init__(self, engine, tokens: int, seqs: int, width: int, want: int, long_queries: bool,
+                 fresh: bool = False):
         self.engine = engine
-        self.key = (tokens, seqs, width, want, long_queries)
+        self.key = (tokens, seqs, width, want, long_queries, fresh)
         dev = engine.device
         groups = engine.cache.groups
         t, s = tokens, seqs
@@ -74,7 +75,7 @@ class PromptRunner:
             kv_lens=part[6], slots_host=None, cu_tokens_host=None, kv_lens_host=None,
             is_decode=False, max_q_len=t, max_kv_len=width * PAGE,
             # every sequence adds at most one partly filled block
-            query_blocks_bound=(t + 63) // 64 + s, long_queries=long_queries)
+            query_blocks_bound=(t + 63) // 64 + s, long_queries=long_queries, fresh=fresh)
         for i, group in enumerate(groups):
             self.ctx._tables[id(group)] = part[7 + i].view(s, width)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -151,7 +152,7 @@ class PromptRunners:
     def __init__(self, engine):
         self.engine = engine
         self.enabled = replay_safe(engine.model)
-        self._runners: Dict[Tuple[int, int, int, int, bool], PromptRunner] = {}
+        self._runners: Dict[Tuple[int, int, int, int, bool, bool], PromptRunner] = {}
 
     def wants(self, steps: Sequence[SequenceStep]) -> bool:
         if not self.enabled or not self.engine.use_graphs or PROMPT_GRAPH_TOKENS <= 0:
@@ -169,7 +170,8 @@ class PromptRunners:
                 width *= 2
         longest = max(plan.cu[i + 1] - plan.cu[i] for i in range(len(plan.slots)))
         key = (token_bucket(int(plan.token_ids.size)), bucket_of(len(plan.slots)), width,
-               bucket_of(len(plan.want_rows)) if plan.want_rows else 0, longest >= 64)
+               bucket_of(len(plan.want_rows)) if plan.want_rows else 0, longest >= 64,
+               all(plan.kv_lens[i] == plan.cu[i + 1] - plan.cu[i] for i in range(len(plan.slots))))
         runner = self._runners.pop(key, None)
         if runner is None:
             if len(self._runners) >= MAX_RUNNERS:

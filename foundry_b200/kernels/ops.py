@@ -104,10 +104,14 @@ _SIGNATURES = {
                               c_void_p, c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int,
                               c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_latent_rows": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
-                       c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int,
-                       c_int, c_int, c_int, c_void_p],
+                       c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_void_p, c_int,
+                       c_int, c_int, c_int, c_int, c_void_p],
     "fb_split_rotate": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
-                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "fb_attention_maps": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
+                          c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll,
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                          c_float, c_void_p, c_float, c_float, c_float, c_void_p],
     "fb_attention_prefill_masked": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
                                     c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int,
                                     c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p],
@@ -1716,6 +1720,11 @@ def attention_sink(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache,
               ctx.n_seqs, q_blocks, H, G, dim, float(scale), window, keep_first,
               1 if sink else 0, float(steep), _stream())
         return out
+    if (maps == 2 and not values_in_keys and not window and not sink and steep == 0.0
+            and attention_maps_fits(ctx, q, dim, vdim, maps) and H // G <= 64
+            and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0):
+        return attention_maps_paged(ctx, q, out, page_table, k_cache, v_cache, H, G, dim, vdim,
+                                    maps, scale, softcap, sink_logits, combine)
     splits, partial = 1, 0
     if ctx.is_decode and T > 0:
         seen = ctx.max_kv_len if not window else min(ctx.max_kv_len, window + keep_first)
@@ -1767,11 +1776,16 @@ def q_temp_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, coef: float, ever
 
 def latent_rows(x: torch.Tensor, a_out: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor,
                 eps: float, freq: torch.Tensor, rot_dims: int, positions, seq_of_token, page_table,
-                cache: torch.Tensor, nb: int, nrot: int, write_cache: bool = True) -> torch.Tensor:
+                cache: torch.Tensor, nb: int, nrot: int, write_cache: bool = True,
+                rows_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x: float32 rows [a | b (nb) | rot (nrot)]. a_out = rmsnorm(a) * wa; the token's
     cache row ([pages, 1, PAGE, nb + nrot]) = [rmsnorm(b) * wb | rot with its first
-    `rot_dims` elements turned in neighbouring pairs by position * freq]."""
+    `rot_dims` elements turned in neighbouring pairs by position * freq]; `rows_out`
+    [T, nb + nrot] receives the same rows in the step's order."""
     T, na = a_out.shape
+    if rows_out is not None and (tuple(rows_out.shape) != (T, nb + nrot)
+                                 or rows_out.dtype != a_out.dtype):
+        raise KernelError("latent_rows: rows_out does not fit")
     if write_cache:
         _check_kv_pair(cache, cache, 1, nb + nrot, nb + nrot, a_out.dtype)
     if freq.dtype != torch.float64 or freq.numel() * 2 < rot_dims:
@@ -1781,26 +1795,91 @@ def latent_rows(x: torch.Tensor, a_out: torch.Tensor, wa: torch.Tensor, wb: torc
           _dev(wb, "wb", torch.float32), float(eps), _dev(freq, "freq", torch.float64), rot_dims,
           _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1],
-          cache.data_ptr() if write_cache else 0, cache.stride(0) if write_cache else 0, T, na, nb,
-          nrot, 1 if write_cache else 0, _stream())
+          cache.data_ptr() if write_cache else 0, cache.stride(0) if write_cache else 0,
+          0 if rows_out is None else _dev(rows_out, "rows_out"), T, na, nb, nrot,
+          1 if write_cache else 0, _stream())
     return a_out
 
 
-def split_rotate(q: torch.Tensor, plain_out: torch.Tensor, wide_out: torch.Tensor, offset: int,
-                 freq: torch.Tensor, rot_dims: int, positions, seq_of_token, H: int, d: int,
-                 c: int) -> None:
+def split_rotate(q: torch.Tensor, plain_out: Optional[torch.Tensor], wide_out: torch.Tensor,
+                 offset: int, freq: torch.Tensor, rot_dims: int, positions, seq_of_token, H: int,
+                 d: int, c: int) -> None:
     """q: float32 rows of H heads [plain (d) | rot (c)]. plain_out [T, H * d] takes the
-    plain parts; wide_out [T, H, wide] takes the rotated parts at [offset, offset + c)."""
+    plain parts; wide_out [T, H, wide] takes the rotated parts at [offset, offset + c).
+    Without `plain_out` (and offset = d) the plain parts go to wide_out[..., :d]."""
     T = q.shape[0]
     wide = wide_out.shape[2]
-    if tuple(plain_out.shape) != (T, H * d) or tuple(wide_out.shape[:2]) != (T, H) \
-            or plain_out.dtype != wide_out.dtype or freq.dtype != torch.float64:
+    if tuple(wide_out.shape[:2]) != (T, H) or freq.dtype != torch.float64 or (
+            plain_out is not None and (tuple(plain_out.shape) != (T, H * d)
+                                       or plain_out.dtype != wide_out.dtype)):
         raise KernelError("split_rotate: shapes differ")
     _call("fb_split_rotate", _dev(q, "q", torch.float32, contiguous=False), _rows(q, "q"),
-          _dev(plain_out, "plain_out"), _dev(wide_out, "wide_out"), code_of(plain_out.dtype), wide,
-          offset, _dev(freq, "freq", torch.float64), rot_dims,
+          0 if plain_out is None else _dev(plain_out, "plain_out"), _dev(wide_out, "wide_out"),
+          code_of(wide_out.dtype), wide, offset, _dev(freq, "freq", torch.float64), rot_dims,
           _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
-          T, H, d, c, _stream())
+          T, H, d, c, 1 if plain_out is None else 0, _stream())
+
+
+# (key size per map, value size) pairs of the tensor-core prompt kernel of
+# csrc/attention_maps_mma.cu, by the number of maps
+MAPS_TC_SIZES = {2: {(16, 32), (32, 32), (32, 64), (64, 64), (64, 128)},
+                 1: {(48, 16), (48, 32), (80, 64), (96, 64), (192, 128)}}
+MAPS_ATTENTION_TC = _os.environ.get("FOUNDRY_B200_MAPS_ATTENTION_TC", "1") != "0"
+
+
+def _query_blocks(ctx) -> int:
+    if ctx.query_blocks_bound is not None:
+        return ctx.query_blocks_bound
+    cu = ctx.cu_tokens_host
+    return sum((cu[i + 1] - cu[i] + 63) // 64 for i in range(ctx.n_seqs))
+
+
+def attention_maps_fits(ctx, q: torch.Tensor, dim: int, vdim: int, maps: int) -> bool:
+    """Whether the step is a prompt step in bfloat16 of sizes the tensor-core kernel has."""
+    return (MAPS_ATTENTION_TC and not ctx.is_decode and q.dtype == torch.bfloat16
+            and (dim, vdim) in MAPS_TC_SIZES.get(maps, ()))
+
+
+def attention_maps_paged(ctx, q, out, page_table, k_cache, v_cache, H: int, G: int, dim: int,
+                         vdim: int, maps: int, scale: float, softcap: float, sink_logits,
+                         combine) -> torch.Tensor:
+    """The tensor-core prompt kernel over the paged cache (key rows of maps * dim)."""
+    lam, post_eps, post_scale = combine if combine is not None else (0.0, 0.0, 1.0)
+    _call("fb_attention_maps", _dev(q, "q", torch.bfloat16, contiguous=False), _rows(q, "q"),
+          _dev(out, "out", torch.bfloat16, contiguous=False), _rows(out, "out"),
+          _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.kv_lens, "kv_lens", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(), 0,
+          v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), v_cache.stride(0),
+          v_cache.stride(1), maps * dim, 0, vdim, 1, maps * dim, ctx.n_seqs, _query_blocks(ctx),
+          H, G, dim, vdim, maps, float(scale), float(softcap),
+          0 if sink_logits is None else _dev(sink_logits, "sink_logits", torch.float32),
+          float(lam), float(post_eps), float(post_scale), _stream())
+    return out
+
+
+def attention_maps_rows(ctx, q: torch.Tensor, out: torch.Tensor, k: torch.Tensor,
+                        k_shared: Optional[torch.Tensor], v: torch.Tensor, H: int, dim: int,
+                        vdim: int, scale: float, softcap: float = 0.0,
+                        sink_logits: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same kernel over the step's own rows, for a step in which every sequence
+    begins at its first token: k [T, H, k1] (a view; a head's own key elements),
+    k_shared [T, dim - k1] (a view; the rest of every head's key), v [T, H, vdim] (a view)."""
+    T = q.shape[0]
+    k1 = k.shape[2]
+    if k.shape[:2] != (T, H) or v.shape != (T, H, vdim) or (k1 != dim) != (k_shared is not None) \
+            or k.stride(2) != 1 or v.stride(2) != 1 or (k_shared is not None and (
+                tuple(k_shared.shape) != (T, dim - k1) or k_shared.stride(1) != 1)):
+        raise KernelError("attention_maps_rows: shapes differ")
+    _call("fb_attention_maps", _dev(q, "q", torch.bfloat16, contiguous=False), _rows(q, "q"),
+          _dev(out, "out", torch.bfloat16, contiguous=False), _rows(out, "out"),
+          _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.kv_lens, "kv_lens", torch.int32),
+          0, 0, k.data_ptr(), 0 if k_shared is None else k_shared.data_ptr(), v.data_ptr(),
+          0, k.stride(1), 0, v.stride(1), k.stride(0),
+          0 if k_shared is None else k_shared.stride(0), v.stride(0), 0, k1, ctx.n_seqs,
+          _query_blocks(ctx), H, H, dim, vdim, 1, float(scale), float(softcap),
+          0 if sink_logits is None else _dev(sink_logits, "sink_logits", torch.float32),
+          0.0, 0.0, 1.0, _stream())
+    return out
 
 
 # ---------------------------------------------------- mixers with a carried state

@@ -17,9 +17,15 @@ expansions are folded into the query and the output,
 
     q_plain . (Wuk_h c) = (Wuk_h^T q_plain) . c,    sum p (Wuv_h c) = Wuv_h (sum p c),
 
-so every step, whatever it brings, is an attention of all heads over the one
+so a step, whatever it brings, is an attention of all heads over the one
 cached row per token (key size kv_rank + rot_dim, the value its first kv_rank
 elements) between two small per-head products.
+
+A prompt step in which every sequence begins at its first token sees only its
+own rows. In bfloat16, at head sizes the tensor-core kernel has, it expands
+them instead (one product for k_plain | v of all heads) and runs the heads as
+ordinary attention with keys of dim + rot_dim and values of vdim, which costs a
+third of the operations of the folded form; the cache rows are written all the same.
 """
 from __future__ import annotations
 
@@ -32,6 +38,7 @@ from ..cache.store import KVRequest, KVView
 from ..kernels import ops
 from ..weights.loader import ExpectedTensor
 from .base import Fetch, Part, register_mixer
+from .linear import matmul_nt
 from .products import product_f32
 
 
@@ -80,6 +87,8 @@ class LatentAttention(Part):
         # per head: [r, d] so that (plain query) x this^T is the query against the latent
         self.uk_t = f("uk").view(H, d, r).transpose(1, 2).contiguous()
         self.uv = f("uv").view(H, e, r).contiguous()
+        # per head [k_plain rows | v rows]: one product expands a step's latent rows
+        self.expand = torch.cat([f("uk").view(H, d, r), self.uv], 1).reshape(H * (d + e), r).contiguous()
         self.q_norm = f("dq.norm").to(torch.float32).contiguous()
         self.kv_norm = f("dkv.norm").to(torch.float32).contiguous()
         self.sink_logits = f("sink").to(torch.float32).contiguous() if self.sink else None
@@ -101,10 +110,24 @@ class LatentAttention(Part):
         table = ctx.page_table(cache.group)
         down = product_f32(x, self.down)  # [T, q_rank | kv_rank | rot_dim]
         cq = torch.empty((T, self.q_rank), **act)
+        expanded = (getattr(ctx, "fresh", False) and r % 8 == 0 and c % 8 == 0 and d % 8 == 0
+                    and e % 8 == 0 and ops.attention_maps_fits(ctx, cq, d + c, e, 1))
+        rows = torch.empty((T, self.row), **act) if expanded else None
         ops.latent_rows(down, cq, self.q_norm, self.kv_norm, self.eps, self.freq, self.rot_dims,
                         ctx.positions, ctx.seq_of_token, table, cache.k, r, c,
-                        write_cache=cache.writes)
+                        write_cache=cache.writes, rows_out=rows)
         q = product_f32(cq, self.uq)  # [T, H (d + c)]
+        if expanded:
+            q_full = torch.empty((T, H, d + c), **act)
+            ops.split_rotate(q, None, q_full, d, self.freq, self.rot_dims, ctx.positions,
+                             ctx.seq_of_token, H, d, c)
+            kv = torch.empty((T, H, d + e), **act)
+            matmul_nt(rows[:, :r], self.expand, kv.view(T, H * (d + e)))
+            out = torch.empty((T, H * e), **act)
+            ops.attention_maps_rows(ctx, q_full.view(T, H * (d + c)), out, kv[:, :, :d],
+                                    rows[:, r:], kv[:, :, d:], H, d + c, e, self.scale,
+                                    sink_logits=self.sink_logits)
+            return product_f32(out, self.o)
         q_plain = torch.empty((T, H * d), **act)
         q_wide = torch.empty((T, H, self.row), **act)
         ops.split_rotate(q, q_plain, q_wide, r, self.freq, self.rot_dims, ctx.positions,

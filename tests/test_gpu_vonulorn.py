@@ -196,52 +196,57 @@ PLACES = [  # (query position, marker position): page borders, the first tokens,
 ]
 
 
-def crafted_differential(W):
+def crafted_differential(W, d=4, e=4):
     """Map 1's query reads input 1 and its key input 2; map 2 reads nothing (all its
     scores are equal: the mean of the values); values are inputs 4..8."""
-    m = {"heads": 1, "kv_heads": 1, "dim": 4, "vdim": 4, "scale": 24.0, "softcap": 40.0,
+    m = {"heads": 1, "kv_heads": 1, "dim": d, "vdim": e, "scale": 24.0, "softcap": 40.0,
          "diff": 0.5, "q_temp": {"coef": 0.1, "every": 64}}
-    q, k = torch.zeros(8, W), torch.zeros(8, W)
+    q, k = torch.zeros(2 * d, W), torch.zeros(2 * d, W)
     q[0, 1] = k[0, 2] = 1.0
-    val = torch.zeros(4, W)
-    val[:, 4:8] = torch.eye(4)
-    out = torch.zeros(W, 4)
-    out[:4] = torch.eye(4)
-    z = torch.zeros(4)
+    val = torch.zeros(e, W)
+    val[:4, 4:8] = torch.eye(4)
+    out = torch.zeros(W, e)
+    out[:4, :4] = torch.eye(4)
+    z = torch.zeros(d)
     return m, {"a.q": q, "a.k": k, "a.v": val, "a.o": out, "a.lq1": z, "a.lk1": z,
                "a.lq2": z, "a.lk2": z}
 
 
-def crafted_latent(W):
+def crafted_latent(W, d=4, c=4, e=4):
     """The query reads input 1 through its latent, the key input 2 of the cached latent,
     values the latent's elements 4..8; the rotated parts are idle in the scores (their
     query rows are zero) but are written and read all the same."""
-    m = {"heads": 1, "dim": 4, "rot_dim": 4, "vdim": 4, "kv_rank": 8, "q_rank": W, "scale": 5.0,
-         "rot": {"base": 100.0, "dims": 4}}
-    uq = torch.zeros(8, W)
+    m = {"heads": 1, "dim": d, "rot_dim": c, "vdim": e, "kv_rank": 8, "q_rank": W, "scale": 5.0,
+         "rot": {"base": 100.0, "dims": c}}
+    uq = torch.zeros(d + c, W)
     uq[0, 1] = 1.0
-    dkv = torch.zeros(12, W)
+    dkv = torch.zeros(8 + c, W)
     dkv[:8, :8] = torch.eye(8)
-    dkv[8:, 8:12] = torch.eye(4)
-    uk, uv = torch.zeros(4, 8), torch.zeros(4, 8)
+    dkv[8:, 8:8 + c] = torch.eye(c)
+    uk, uv = torch.zeros(d, 8), torch.zeros(e, 8)
     uk[0, 2] = 1.0
-    uv[:, 4:] = torch.eye(4)
-    out = torch.zeros(W, 4)
-    out[:4] = torch.eye(4)
+    uv[:4, 4:] = torch.eye(4)
+    out = torch.zeros(W, e)
+    out[:4, :4] = torch.eye(4)
     return m, {"a.dq": torch.eye(W), "a.dq.norm": torch.ones(W), "a.uq": uq, "a.dkv": dkv,
                "a.dkv.norm": torch.ones(8), "a.uk": uk, "a.uv": uv, "a.sink": torch.tensor([2.0]),
                "a.o": out}
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sizes", ["small", "tensor-core"])
 @pytest.mark.parametrize("kind", ["attention", "latent_attention"])
-def test_one_key_that_stands_out_is_found_wherever_it_lies(kind, dtype):
+def test_one_key_that_stands_out_is_found_wherever_it_lies(kind, sizes, dtype):
     """Crafted mixers in which one key dominates one query: at the first tokens, on both
     sides of page borders, hundreds of tokens back; as the last token of a prompt and
-    as a token decoded alone."""
+    as a token decoded alone. Once at sizes that only the CUDA-core kernel takes, once at
+    sizes whose prompts run on the tensor cores in bfloat16."""
     from foundry_b200.cache import SequenceCache
-    W = 16
-    m, weights = crafted_differential(W) if kind == "attention" else crafted_latent(W)
+    W = 32
+    if kind == "attention":
+        m, weights = crafted_differential(W) if sizes == "small" else crafted_differential(W, 16, 32)
+    else:
+        m, weights = crafted_latent(W) if sizes == "small" else crafted_latent(W, 32, 16, 16)
     part = mixer_part(kind, m, W, 1e-6, weights, dtype)
     cache = SequenceCache({0: part.cache_request()}, 2048, 2, dtype, DEV)
     for query_at, marker_at in PLACES:
