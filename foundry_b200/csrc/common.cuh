@@ -164,6 +164,14 @@ __device__ __forceinline__ __nv_bfloat16 fb_from_float<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
 }
 
+// The activation of a gated feed-forward on its gate: 0 SiLU, g / (1 + exp(-g));
+// 1 the tanh form of GELU, 0.5 g (1 + tanh(u)) with u = sqrt(2/pi) (g + 0.044715 g^3),
+// which is g / (1 + exp(-2u)).
+__device__ __forceinline__ float fb_glu_act(float g, int act) {
+  const float z = act == 0 ? g : 1.5957691216057308f * (g + 0.044715f * g * g * g);
+  return g / (1.0f + __expf(-z));
+}
+
 __device__ __forceinline__ float fb_warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -91,6 +91,7 @@ struct RowsParams {
   long long ldo;
   int out_f32;
   int epilogue;
+  int glu_act;          // epilogue 1: the gate's activation (0 SiLU, 1 GELU in its tanh form)
   int vector_ok;        // the epilogue's rows are aligned for 16- and 8-byte accesses
   RowsScale scale;
   RowsSink sink;
@@ -402,8 +403,8 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         } else if (epi == 1) {
           // (gate, up) pairs: two results per lane
           __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (long long)j * p.ldo + (f0 >> 1);
-          const float h0 = val[0] / (1.0f + __expf(-val[0])) * val[1];
-          const float h1 = val[2] / (1.0f + __expf(-val[2])) * val[3];
+          const float h0 = fb_glu_act(val[0], p.glu_act) * val[1];
+          const float h1 = fb_glu_act(val[2], p.glu_act) * val[3];
           if (vec) {
             const __nv_bfloat162 pk = __floats2bfloat162_rn(h0, h1);
             *reinterpret_cast<__nv_bfloat162*>(dst) = pk;
@@ -557,8 +558,12 @@ FB_API int fb_gemm_rows(const void* x, long long ldx, int M, const void* w, long
                  ((uintptr_t)w % 16) == 0,
              "gemm_rows: K and the row strides must be multiples of 8 elements and the operands "
              "16-byte aligned (K=%d ldx=%lld ldw=%lld)", K, ldx, ldw);
+  // epilogue 4: as 1 with the tanh form of GELU on the gate
+  const int glu_act = epilogue == 4 ? 1 : 0;
+  if (epilogue == 4) epilogue = 1;
   FB_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_rows: unknown epilogue %d", epilogue);
   RowsParams p{};
+  p.glu_act = glu_act;
   p.M = M; p.N = N; p.K = K;
   const int tiles = (N + BM - 1) / BM;
   p.kblocks = (K + BK - 1) / BK;

@@ -455,7 +455,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
         gate *= rs;
         up *= rs;
         out_h[(size_t)tok * ldo + (n0 >> 1) + p] =
-            __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+            __float2bfloat16_rn(fb_glu_act(gate, epilogue == 4 ? 1 : 0) * up);
       }
     }
   }
@@ -483,7 +483,7 @@ int launch_skinny(const void* x, long long ldx, const void* w, long long ldw, vo
   FB_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)x % 16) == 0 &&
                  ((uintptr_t)w % 16) == 0,
              "gemm_skinny: K, the row strides and the pointers must keep 16-byte alignment");
-  FB_REQUIRE(epilogue != 1 || (!out_f32 && N % 2 == 0),
+  FB_REQUIRE((epilogue != 1 && epilogue != 4) || (!out_f32 && N % 2 == 0),
              "gemm_skinny: the SiLU-mul epilogue needs a bf16 output and an even row count");
   FB_REQUIRE(ksplit >= 1 && ksplit <= 64 && (ksplit == 1 || (out_f32 && epilogue == 0 &&
                                                              plane_stride >= (long long)T * ldo)),
@@ -566,7 +566,8 @@ FB_API int fb_gemm_skinny(const void* x, long long ldx, const void* w, long long
                           long long plane_stride, int warps, const float* scale_ss,
                           int scale_count, int scale_stride, int scale_dim, float scale_eps,
                           cudaStream_t stream) {
-  FB_REQUIRE(epilogue == 0 || epilogue == 1, "gemm_skinny: epilogue %d", epilogue);
+  // epilogue 4: as 1 with the tanh form of GELU on the gate
+  FB_REQUIRE(epilogue == 0 || epilogue == 1 || epilogue == 4, "gemm_skinny: epilogue %d", epilogue);
   const RowScale scale{scale_ss, scale_count, scale_stride,
                        scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps};
   return launch_skinny(x, ldx, w, ldw, out, ldo, out_f32, T, N, K, epilogue, next, next_bytes,

@@ -448,6 +448,9 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   FB_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0,
              "gemm_tc: operands must start on 16-byte boundaries");
   FB_REQUIRE(splits >= 1 && (splits == 1 || out_f32), "gemm_tc: split-K needs a float32 output");
+  // epilogue 4: as 1 with the tanh form of GELU on the gate
+  const int glu_act = epilogue == 4 ? 1 : 0;
+  if (epilogue == 4) epilogue = 1;
   FB_REQUIRE(epilogue == 0 || epilogue == 2 ||
                  (epilogue == 1 && splits == 1 && !out_f32 && (stride_a == 1 || stride_b == 1)),
              "gemm_tc: the SiLU-mul epilogue needs one split, a bf16 output and features on a "
@@ -465,7 +468,7 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
   p.kblocks_per_split = (total_kb + splits - 1) / splits;
   p.stride_a = stride_a; p.stride_b = stride_b; p.split_stride = split_stride;
-  p.out = out; p.out_f32 = out_f32; p.epilogue = epilogue;
+  p.out = out; p.out_f32 = out_f32; p.epilogue = epilogue; p.glu_act = glu_act;
   p.constant_operand = constant_operand;
   p.full_tiles = 0; p.tail_splits = 1; p.tail_kblocks = total_kb; p.partial = nullptr;
   p.tail_counters = nullptr;
@@ -563,7 +566,7 @@ FB_API int fb_gemm_tc_rope(const void* x, long long ldx, int T, const void* w, l
   p.rows_a = T; p.rows_b = (write_cache ? A + 2 * Kh : A) * D; p.K = K;  // w holds only the rows that are wanted
   p.kblocks_per_split = total_kb;
   p.stride_a = ldq; p.stride_b = 1; p.split_stride = 0;
-  p.out = q_out; p.out_f32 = 0; p.epilogue = 3;
+  p.out = q_out; p.out_f32 = 0; p.epilogue = 3; p.glu_act = 0;
   p.constant_operand = 2;
   p.full_tiles = 0; p.tail_splits = 1; p.tail_kblocks = total_kb; p.partial = nullptr;
   p.tail_counters = nullptr;

@@ -56,7 +56,8 @@ struct FbGemmParams {
   void* out;
   int out_f32;                // 1: float32 output, 0: bfloat16
   int constant_operand;       // 1: A holds constants (weights), 2: B does, 0: neither
-  int epilogue;               // 0: store D; 1: SiLU(gate) * up over interleaved feature pairs;
+  int glu_act;                // epilogue 1: the gate's activation (0 SiLU, 1 GELU in its tanh form)
+  int epilogue;               // 0: store D; 1: act(gate) * up over interleaved feature pairs;
                               // 2: residual add in front of a norm (`rows`)
                               // 3: rotation and cache write of a q/k/v projection (`rope`)
   FbRowExtras rows;
@@ -103,7 +104,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const float gate = v[e + 2 * q];
-              r8[q] = gate / (1.0f + __expf(-gate)) * v[e + 2 * q + 1];
+              r8[q] = fb_glu_act(gate, p.glu_act) * v[e + 2 * q + 1];
             }
             uint4 pk;
             __nv_bfloat162 h0 = __floats2bfloat162_rn(r8[0], r8[1]);
@@ -122,7 +123,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
             if (j0 + e + 1 < p.rows_b) {
               const float gate = v[e];
               out_h[base + (e >> 1)] =
-                  __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * v[e + 1]);
+                  __float2bfloat16_rn(fb_glu_act(gate, p.glu_act) * v[e + 1]);
             }
           }
         }
@@ -135,7 +136,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
         if ((lane & 1) == 0 && i_global + 1 < p.rows_a && j0 + e < p.rows_b) {
           const float gate = v[e];
           out_h[(i_global >> 1) + (j0 + e) * p.stride_b] =
-              __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * other);
+              __float2bfloat16_rn(fb_glu_act(gate, p.glu_act) * other);
         }
       }
     }

@@ -453,6 +453,8 @@ def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
 
 
 GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+# the products' epilogue code for act(gate) * up over (gate, up) row pairs
+GLU_EPILOGUE = {"silu": 1, "gelu_tanh": 4}
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False,
@@ -896,17 +898,18 @@ def _gemm_rows(x, w, epilogue: int, out=None, sink: Optional[ResidualSink] = Non
 
 
 def gemm_rows(x, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-              out_dtype: Optional[torch.dtype] = None, silu_mul: bool = False) -> torch.Tensor:
+              out_dtype: Optional[torch.dtype] = None, silu_mul: bool = False,
+              act: str = "silu") -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T for 17 to 256 token rows (any count up to
     256 works); with `silu_mul` the weight rows are (gate, up) pairs and out is
-    [M, N / 2]. `x` may be a `RowScaled`."""
+    [M, N / 2] = act(gate) * up. `x` may be a `RowScaled`."""
     M, N = x.shape[0], w.shape[0]
     if out is None:
         out = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype or torch.bfloat16,
                           device=w.device)
     if tuple(out.shape) != (M, N // 2 if silu_mul else N) or out.stride(1) != 1:
         raise KernelError(f"gemm_rows: out is {tuple(out.shape)} for x {tuple(x.shape)}, w {tuple(w.shape)}")
-    _gemm_rows(x, w, 1 if silu_mul else 0, out=out)
+    _gemm_rows(x, w, GLU_EPILOGUE[act] if silu_mul else 0, out=out)
     return out
 
 
@@ -1312,36 +1315,32 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
 def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor,
                        then_reads: Optional[torch.Tensor] = None, act: str = "silu") -> torch.Tensor:
     """out[M, I] = act(x @ gate^T) * (x @ up^T) with `w_pairs` [2I, K] holding
-    gate i in row 2i and up i in row 2i+1; with SiLU the activation runs in the
-    product's epilogue, so the [M, 2I] intermediate never reaches memory. Another
-    activation runs behind the product, on its float32 result."""
+    gate i in row 2i and up i in row 2i+1; the activation ("silu", "gelu_tanh")
+    runs in the product's epilogue, so the [M, 2I] intermediate never reaches memory."""
     M, K = x.shape
     two_i = w_pairs.shape[0]
     if out.shape != (M, two_i // 2) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise KernelError("gemm_bf16_silu_mul: out must be [M, I] bfloat16 with contiguous rows")
     if M == 0:
         return out
-    if act != "silu":
-        tmp = torch.empty((M, two_i), dtype=torch.float32, device=out.device)
-        gemm_bf16(x, w_pairs, tmp)
-        return silu_mul(tmp, out, interleaved=True, act=act)
+    epilogue = GLU_EPILOGUE[act]
     usable = _tc_usable(x.values if isinstance(x, RowScaled) else x, w_pairs, out)
     if usable and rows_usable(x, w_pairs):
-        return gemm_rows(x, w_pairs, out, silu_mul=True)
+        return gemm_rows(x, w_pairs, out, silu_mul=True, act=act)
     if not usable:
         x = plain(x)
         tmp = torch.empty((M, two_i), dtype=torch.bfloat16, device=x.device)
         gemm_simt(x, w_pairs, tmp)
-        return silu_mul(tmp, out, interleaved=True)
+        return silu_mul(tmp, out, interleaved=True, act=act)
     if M <= SKINNY_ROWS:
-        return gemm_skinny(x, w_pairs, out, epilogue=1, then_reads=then_reads,
+        return gemm_skinny(x, w_pairs, out, epilogue=epilogue, then_reads=then_reads,
                            warps=skinny_plan(two_i, K, False)[1])
     if M > 128:
         bn, form = prompt_plan(M, two_i)
-        gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1, constant_operand=2,
+        gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=epilogue, constant_operand=2,
                 persistent=form)
     else:
-        gemm_tc(x, w_pairs, out, out.stride(0), 1, 128, epilogue=1, constant_operand=2)
+        gemm_tc(x, w_pairs, out, out.stride(0), 1, 128, epilogue=epilogue, constant_operand=2)
     return out
 
 
