@@ -193,12 +193,17 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
           const float* qm = qs + mm * D;
           const T* km = krow + mm * D;
           float dot = 0.f;
-          if (kvec) {  // key rows of whole 16-byte pieces
-            for (int d = 0; d < D; d += 8) {
-              float kv[8];
-              load8<T>(km + d, kv);
+          if (kvec) {  // key rows of whole 16-byte pieces, four loads in flight at a time
+            for (int d = 0; d < D; d += 32) {
+              float kv[4][8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) dot = fmaf(qm[d + e], kv[e], dot);
+              for (int u = 0; u < 4; ++u)
+                if (d + u * 8 < D) load8<T>(km + d + u * 8, kv[u]);
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (d + u * 8 < D)
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) dot = fmaf(qm[d + u * 8 + e], kv[u][e], dot);
             }
           } else {
             for (int d = 0; d < D; ++d) dot = fmaf(qm[d], fb_load_coherent<T>(km + d), dot);
@@ -220,24 +225,42 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
       const int n = min(32, end - j0);
       if (VEC) {
         const int sub = lane / lpr, ks = 32 / lpr;
-        for (int jj = 0; jj < n; jj += ks) {  // uniform trip count; lanes past n add nothing
-          const int key = jj + sub;
-          float pj[MAPS];
+        // U groups of keys at a time, the loads of all of them issued before the first sum:
+        // a lane's loads of one key after another would each wait out the memory's latency
+        constexpr int U = PIECES == 1 ? 4 : 2;
+        for (int jj = 0; jj < n; jj += U * ks) {  // uniform trip count; lanes past n add nothing
+          float pj[U][MAPS];
+          long long off[U];
+          float vv[U][PIECES][8];
 #pragma unroll
-          for (int mm = 0; mm < MAPS; ++mm) pj[mm] = __shfl_sync(0xffffffffu, p[mm], key & 31);
-          const long long off = __shfl_sync(0xffffffffu, v_off, key & 31);
+          for (int u = 0; u < U; ++u) {
+            const int key = jj + u * ks + sub;
 #pragma unroll
-          for (int pc = 0; pc < PIECES; ++pc) {
-            const int d0 = ((lane % lpr) + pc * lpr) * 8;
-            if (key < n && d0 < VD) {
-              float vv[8];
-              load8<T>(vbase + off + d0, vv);
+            for (int mm = 0; mm < MAPS; ++mm) {
+              pj[u][mm] = __shfl_sync(0xffffffffu, p[mm], key & 31);
+              if (key >= n) pj[u][mm] = 0.f;
+            }
+            off[u] = __shfl_sync(0xffffffffu, v_off, key & 31);
+#pragma unroll
+            for (int pc = 0; pc < PIECES; ++pc) {
+              const int d0 = ((lane % lpr) + pc * lpr) * 8;
+              if (key < n && d0 < VD) {
+                load8<T>(vbase + off[u] + d0, vv[u][pc]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) vv[u][pc][e] = 0.f;
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int pc = 0; pc < PIECES; ++pc)
 #pragma unroll
               for (int mm = 0; mm < MAPS; ++mm)
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[mm][pc * 8 + e] = fmaf(pj[mm], vv[e], acc[mm][pc * 8 + e]);
-            }
-          }
+                for (int e = 0; e < 8; ++e)
+                  acc[mm][pc * 8 + e] = fmaf(pj[u][mm], vv[u][pc][e], acc[mm][pc * 8 + e]);
         }
       } else {
         for (int jj = 0; jj < n; ++jj) {
@@ -309,7 +332,234 @@ attention_sink_kernel(const T* q, long long q_stride, T* __restrict__ out, long 
   }
 }
 
-// One warp per (token, head): the runs' partial results become the output.
+// The same attention with a chunk's 32 key rows (and value rows) staged in shared
+// memory once per block: the warps of a block are query heads that share a key head
+// (the heads of one token), so the rows cross from L2 once per block instead of once
+// per head, in coalesced 16-byte copies; a lane then reads its key's row out of shared
+// memory (rows 16 bytes longer than their data keep those reads free of bank
+// conflicts). For sizes whose rows are whole 16-byte pieces. `v_in_k`: the values are
+// the first VD elements of the key rows, which are staged only once.
+__device__ __forceinline__ void cp_async16_s(void* dst, const void* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_all_s() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+template <typename T>
+__device__ __forceinline__ void load8s(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8s<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8s<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <typename T, int MAPS, int NACC>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_sink_staged_kernel(const T* q, long long q_stride, T* __restrict__ out,
+                             long long out_stride, const int* __restrict__ positions,
+                             const int* __restrict__ seq_of_token,
+                             const int* __restrict__ page_table, int max_pages, const T* k_cache,
+                             const T* v_cache, long long k_page, long long k_head,
+                             long long v_page, long long v_head, int k_row, int v_row,
+                             ScoreRule rule, int H, int G, int D, int VD, int splits,
+                             float* __restrict__ partial, int lpr, int v_in_k) {
+  fb_pdl_wait();
+  extern __shared__ __align__(16) unsigned char staged_smem[];
+  constexpr int PIECES = NACC / 8;
+  constexpr int PAD = 16 / (int)sizeof(T);
+  const int KW = MAPS * D;
+  const int kp = KW + PAD, vp = v_in_k ? kp : VD + PAD;  // row pitches in elements
+  T* sK = reinterpret_cast<T*>(staged_smem);               // [32][kp]
+  T* sV = v_in_k ? sK : sK + 32 * kp;                      // [32][vp]
+  float* qs_all = reinterpret_cast<float*>(sK + 32 * kp + (v_in_k ? 0 : 32 * vp));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* qs = qs_all + (size_t)warp * KW;
+  const int t = blockIdx.x;
+  const int rep = H / G;
+  const int per_g = (rep + WARPS - 1) / WARPS;  // blocks that the query heads of a key head take
+  const int g = blockIdx.y / per_g;
+  const int within = (blockIdx.y % per_g) * WARPS + warp;
+  const bool active = within < rep;             // (an idle warp still helps with the staging)
+  const int a = g * rep + within;
+  const int seq = seq_of_token[t];
+  T* o = out + (size_t)t * out_stride + (size_t)a * VD;
+  if (seq < 0) {  // padding token (the whole block): defined output, no cache access
+    if (active)
+      for (int d = lane; d < VD; d += 32) o[d] = fb_from_float<T>(0.f);
+    return;
+  }
+  const int pos = positions[t];
+  if (active) {
+    const T* qrow = q + (size_t)t * q_stride + (size_t)a * KW;
+    for (int d = lane; d < KW; d += 32) qs[d] = fb_load_coherent<T>(qrow + d);
+  }
+  const float slope = (active && rule.steep > 0.f) ? exp2f(-rule.steep * (float)(a + 1) / (float)H) : 0.f;
+  const int lo = (rule.window > 0 && pos - rule.window + 1 > 0) ? pos - rule.window + 1 : 0;
+  const int kept = min(rule.keep_first, lo);
+  const int* pages = page_table + (size_t)seq * max_pages;
+  const T* kbase = k_cache + (long long)g * k_head;
+  const T* vbase = v_cache + (long long)g * v_head;
+  const int total = kept + (pos + 1 - lo);
+  const int i0 = (int)((long long)total * blockIdx.z / splits);
+  const int i1 = (int)((long long)total * (blockIdx.z + 1) / splits);
+  const bool own_sink = rule.sink && splits == 1;
+  const float sink_score = (active && rule.sink == 2) ? rule.sink_logit[a] : 0.f;
+  float m[MAPS], l[MAPS];
+  float acc[MAPS][NACC];
+#pragma unroll
+  for (int mm = 0; mm < MAPS; ++mm) {
+    m[mm] = own_sink ? sink_score : -INFINITY;
+    l[mm] = own_sink ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[mm][i] = 0.f;
+  }
+  const int units_k = KW * (int)sizeof(T) / 16, units_v = VD * (int)sizeof(T) / 16;
+
+  for (int range = 0; range < 2; ++range) {
+    const int begin = range == 0 ? min(i0, kept) : lo + max(i0 - kept, 0);
+    const int end = range == 0 ? min(i1, kept) : lo + max(i1 - kept, 0);  // exclusive
+    for (int j0 = begin; j0 < end; j0 += 32) {
+      const int n = min(32, end - j0);
+      __syncthreads();  // the rows of the chunk before have been read by every warp
+      for (int id = threadIdx.x; id < n * units_k; id += WARPS * 32) {
+        const int r = id / units_k, u = id - r * units_k;
+        const int j = j0 + r;
+        const char* src = reinterpret_cast<const char*>(
+            kbase + (long long)pages[j / FB_PAGE] * k_page + (long long)(j % FB_PAGE) * k_row);
+        cp_async16_s(reinterpret_cast<char*>(sK + (size_t)r * kp) + u * 16, src + u * 16);
+      }
+      if (!v_in_k) {
+        for (int id = threadIdx.x; id < n * units_v; id += WARPS * 32) {
+          const int r = id / units_v, u = id - r * units_v;
+          const int j = j0 + r;
+          const char* src = reinterpret_cast<const char*>(
+              vbase + (long long)pages[j / FB_PAGE] * v_page + (long long)(j % FB_PAGE) * v_row);
+          cp_async16_s(reinterpret_cast<char*>(sV + (size_t)r * vp) + u * 16, src + u * 16);
+        }
+      }
+      cp_async_all_s();
+      __syncthreads();
+      if (!active) continue;
+      const int j = j0 + lane;
+      float s[MAPS], p[MAPS];
+#pragma unroll
+      for (int mm = 0; mm < MAPS; ++mm) {
+        s[mm] = -INFINITY;
+        if (lane < n) {
+          const float* qm = qs + mm * D;
+          const T* km = sK + (size_t)lane * kp + mm * D;
+          float d0 = 0.f, d1 = 0.f;  // two sums side by side: shorter chains
+          for (int d = 0; d < D; d += 16) {
+            float ka[8], kb[8], qa[8], qb[8];
+            load8s<T>(km + d, ka);
+            load8s<float>(qm + d, qa);  // (all lanes read the same query elements: a broadcast)
+            if (d + 8 < D) {
+              load8s<T>(km + d + 8, kb);
+              load8s<float>(qm + d + 8, qb);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) d0 = fmaf(qa[e], ka[e], d0);
+            if (d + 8 < D)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) d1 = fmaf(qb[e], kb[e], d1);
+          }
+          s[mm] = capped((d0 + d1) * rule.scale, rule.softcap) - slope * (float)(pos - j);
+        }
+        const float m_new = fmaxf(m[mm], fb_warp_max(s[mm]));
+        const float corr = expf(m[mm] - m_new);
+        p[mm] = (lane < n) ? expf(s[mm] - m_new) : 0.f;
+        l[mm] = l[mm] * corr + fb_warp_sum(p[mm]);
+        m[mm] = m_new;
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[mm][i] *= corr;
+      }
+      const int sub = lane / lpr, ks = 32 / lpr;
+      for (int jj = 0; jj < n; jj += ks) {  // uniform trip count; lanes past n add nothing
+        const int key = jj + sub;
+        float pj[MAPS];
+#pragma unroll
+        for (int mm = 0; mm < MAPS; ++mm) pj[mm] = __shfl_sync(0xffffffffu, p[mm], key & 31);
+#pragma unroll
+        for (int pc = 0; pc < PIECES; ++pc) {
+          const int d0 = ((lane % lpr) + pc * lpr) * 8;
+          if (key < n && d0 < VD) {
+            float vv[8];
+            load8s<T>(sV + (size_t)key * vp + d0, vv);
+#pragma unroll
+            for (int mm = 0; mm < MAPS; ++mm)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[mm][pc * 8 + e] = fmaf(pj[mm], vv[e], acc[mm][pc * 8 + e]);
+          }
+        }
+      }
+    }
+  }
+  if (!active) return;
+#pragma unroll
+  for (int mm = 0; mm < MAPS; ++mm)
+#pragma unroll
+    for (int e = 0; e < NACC; ++e)
+      for (int off = lpr; off < 32; off <<= 1)
+        acc[mm][e] += __shfl_xor_sync(0xffffffffu, acc[mm][e], off);
+  auto place = [&](int i) { return ((lane % lpr) + (i / 8) * lpr) * 8 + (i % 8); };
+  const bool writer = lane < lpr;
+  if (splits > 1) {
+#pragma unroll
+    for (int mm = 0; mm < MAPS; ++mm) {
+      float* dst = partial + ((((size_t)t * H + a) * splits + blockIdx.z) * MAPS + mm) * (VD + 2);
+      if (lane == 0) { dst[0] = m[mm]; dst[1] = l[mm]; }
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) {
+        const int d = place(i);
+        if (writer && d < VD) dst[2 + d] = acc[mm][i];
+      }
+    }
+    return;
+  }
+  if (MAPS == 1) {
+    const float inv_l = 1.0f / l[0];
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      const int d = place(i);
+      if (writer && d < VD) o[d] = fb_from_float<T>(acc[0][i] * inv_l);
+    }
+    return;
+  }
+  const float inv0 = 1.0f / l[0], inv1 = 1.0f / l[MAPS - 1];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NACC; ++i) {
+    const int d = place(i);
+    acc[0][i] = acc[0][i] * inv0 - rule.lambda * (acc[MAPS - 1][i] * inv1);
+    if (writer && d < VD) ss = fmaf(acc[0][i], acc[0][i], ss);
+  }
+  const float r = rule.post_scale / sqrtf(fb_warp_sum(ss) / (float)VD + rule.post_eps);
+#pragma unroll
+  for (int i = 0; i < NACC; ++i) {
+    const int d = place(i);
+    if (writer && d < VD) o[d] = fb_from_float<T>(acc[0][i] * r);
+  }
+}
+
+// One warp per (token, head): the runs' partial results become the output. Lane s holds
+// run s's maximum and sum (runs s and s + 32 with more than 32 runs), so the statistics
+// are two loads a lane and shuffles; the runs' value rows are then summed with their
+// weights, four runs' loads in flight at a time.
 template <typename T, int MAPS, int NACC>
 __global__ void attention_sink_merge_kernel(const float* partial, T* __restrict__ out,
                                             long long out_stride, const int* __restrict__ seq_of_token,
@@ -325,22 +575,38 @@ __global__ void attention_sink_merge_kernel(const float* partial, T* __restrict_
   for (int mm = 0; mm < MAPS; ++mm) {
     const float* src = partial + (((size_t)t * H + a) * splits * MAPS + mm) * (VD + 2);
     const size_t step = (size_t)MAPS * (VD + 2);  // from one run's record of this map to the next
-    float M = rule.sink ? sink_score : -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(src + s * step));
-    float L = rule.sink ? expf(sink_score - M) : 0.f;
+    float ms[2], ls[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int run = lane + 32 * h;
+      ms[h] = run < splits ? __ldcg(src + run * step) : -INFINITY;
+      ls[h] = run < splits ? __ldcg(src + run * step + 1) : 0.f;
+    }
+    float M = fb_warp_max(fmaxf(ms[0], ms[1]));
+    if (rule.sink) M = fmaxf(M, sink_score);
+    float f[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) f[h] = ms[h] == -INFINITY ? 0.f : expf(ms[h] - M);  // 0: an empty run
+    const float L = fb_warp_sum(ls[0] * f[0] + ls[1] * f[1]) + (rule.sink ? expf(sink_score - M) : 0.f);
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[mm][i] = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float* ps = src + s * step;
-      const float ms = __ldcg(ps);
-      if (ms == -INFINITY) continue;  // an empty run
-      const float f = expf(ms - M);
-      L = fmaf(__ldcg(ps + 1), f, L);
+    for (int s0 = 0; s0 < splits; s0 += 4) {
+      float w[4], v[4][NACC];
 #pragma unroll
-      for (int i = 0; i < NACC; ++i) {
-        const int d = lane + 32 * i;
-        if (d < VD) acc[mm][i] = fmaf(__ldcg(ps + 2 + d), f, acc[mm][i]);
+      for (int u = 0; u < 4; ++u) {
+        const int run = s0 + u;
+        const float both = __shfl_sync(0xffffffffu, run < 32 ? f[0] : f[1], run & 31);
+        w[u] = run < splits ? both : 0.f;
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) {
+          const int d = lane + 32 * i;
+          v[u][i] = (run < splits && d < VD) ? __ldcg(src + run * step + 2 + d) : 0.f;
+        }
       }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[mm][i] = fmaf(v[u][i], w[u], acc[mm][i]);
     }
     const float inv = 1.0f / L;
 #pragma unroll
@@ -610,7 +876,7 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
   const int kvec = D % 8 == 0 && k_row % 8 == 0 && k_page % 8 == 0 && k_head % 8 == 0 &&
                    ((uintptr_t)k_cache % 32) == 0;
   FB_REQUIRE(window >= 0 && keep_first >= 0 && max_pages > 0, "attention_sink: bad mask");
-  FB_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || partial != nullptr),
+  FB_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || partial != nullptr),
              "attention_sink: %d runs need a workspace", splits);
   if (T == 0) return 0;
   ScoreRule rule{window, keep_first, sink, sink_logit, scale, steep, softcap, lambda, post_eps,
@@ -622,6 +888,32 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
   while (lpr * 8 < VD && lpr < 32) lpr *= 2;  // lanes that share a value row: a power of two
   const size_t smem = (size_t)WARPS * maps * D * 4;
   const bool wide = VD > 256;
+  // Rows of whole 16-byte pieces: the form that stages a chunk's rows in shared memory
+  // once for the query heads of a key head.
+  const int v_in_k = v_cache == k_cache && v_row == k_row && v_page == k_page && v_head == k_head;
+  const int elt = dtype == FB_F32 ? 4 : 2, pad = 16 / elt;
+  const size_t staged_smem = (size_t)32 * (maps * D + pad) * elt +
+                             (v_in_k ? 0 : (size_t)32 * (VD + pad) * elt) +
+                             (size_t)WARPS * maps * D * 4;
+  if (vec && kvec && v_row % 8 == 0 && staged_smem <= 160 * 1024) {
+    const int rep = H / G;
+    dim3 sgrid(T, G * ((rep + WARPS - 1) / WARPS), splits);
+#define FB_STAGED_LAUNCH(MAPS_, NACC_)                                                          \
+    FB_DISPATCH_DTYPE(dtype, E, {                                                               \
+      static bool seen[64];                                                                     \
+      if (staged_smem > 48 * 1024 && fb_first_use_on_device(seen))                              \
+        cudaFuncSetAttribute(attention_sink_staged_kernel<E, MAPS_, NACC_>,                     \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);          \
+      fb_launch(attention_sink_staged_kernel<E, MAPS_, NACC_>, dim3(sgrid), dim3(WARPS * 32),   \
+          staged_smem, stream, (const E*)q, q_stride, (E*)out, out_stride, positions,           \
+          seq_of_token, page_table, max_pages, (const E*)k_cache, (const E*)v_cache, k_page,    \
+          k_head, v_page, v_head, k_row, v_row, rule, H, G, D, VD, splits, partial, lpr,        \
+          v_in_k); })
+    if (maps == 2) FB_STAGED_LAUNCH(2, 8);
+    else if (wide) FB_STAGED_LAUNCH(1, 24);
+    else FB_STAGED_LAUNCH(1, 8);
+#undef FB_STAGED_LAUNCH
+  } else {
 #define FB_SINK_LAUNCH(VEC_, MAPS_, NACC_)                                                       \
   FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_kernel<E, VEC_, MAPS_, NACC_>,          \
       dim3(grid), dim3(WARPS * 32), smem, stream, (const E*)q, q_stride, (E*)out, out_stride,    \
@@ -632,6 +924,7 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
   else if (wide) { if (vec) FB_SINK_LAUNCH(true, 1, 24); else FB_SINK_LAUNCH(false, 1, 24); }
   else { if (vec) FB_SINK_LAUNCH(true, 1, 8); else FB_SINK_LAUNCH(false, 1, 8); }
 #undef FB_SINK_LAUNCH
+  }
   if (splits > 1) {
     int rc = fb_check_launch("attention_sink");
     if (rc) return rc;

@@ -1670,7 +1670,7 @@ def _check_kv_pair(k_cache, v_cache, G, dim, vdim, dtype) -> None:
 
 
 SINK_ATTENTION_TC = _os.environ.get("FOUNDRY_B200_SINK_ATTENTION_TC", "1") != "0"
-SINK_DECODE_WARPS = 2400  # warps a single-token step's attention should come to
+SINK_DECODE_WARPS = 4736  # warps a single-token step's attention should come to (32 an SM)
 
 
 def attention_sink(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache, v_cache, H: int,
