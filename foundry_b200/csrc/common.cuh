@@ -83,6 +83,21 @@ inline cudaError_t fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// A launch without the mark: the kernel starts when everything before it in the stream
+// has finished, and its own `fb_pdl_wait()` returns at once.
+template <typename... KArgs, typename... Args>
+inline cudaError_t fb_launch_serial(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = nullptr;
+  cfg.numAttrs = 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 // The same launch with the grid's z extent grouped into thread-block clusters of
 // `cluster_z` CTAs (distributed shared memory between the CTAs of a cluster).
 template <typename... KArgs, typename... Args>

@@ -126,7 +126,7 @@ _SIGNATURES = {
                       c_void_p],
     "fb_state_scan": [c_int, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll,
                       c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
-                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_float, c_void_p,
                           c_int, c_int, c_int, c_int, c_void_p],
     "fb_unary_cast": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -1986,7 +1986,7 @@ def state_scan(ctx, mode: int, q, k, v, g, state: StateRows, field: str, out: to
           0 if bonus is None else _dev(bonus, "bonus", f32), state.rows.data_ptr(), state.stride,
           state.offset[field], out.data_ptr(), _dev(ctx.cu_tokens, "cu_tokens", torch.int32),
           _dev(ctx.slots, "slots", torch.int32), ctx.n_seqs, H, rep, dim, vdim,
-          1 if decay_per_head else 0, _stream())
+          1 if decay_per_head else 0, 0 if ctx.is_decode else 1, _stream())
     return out
 
 
