@@ -127,6 +127,9 @@ def test_mixers_at_other_sizes(dtype):
                        "softcap": 30.0, "diff": 0.6, "q_temp": {"coef": 0.3, "every": 64}}),
         ("delta", {"heads": 6, "kv_heads": 2, "dim": 8, "vdim": 72, "conv": 5}),
         ("delta", {"heads": 1, "kv_heads": 1, "dim": 128, "vdim": 64, "conv": 1}),
+        # fewer rotated elements than the rotated part holds: the rest passes unchanged
+        ("latent_attention", {"heads": 2, "dim": 16, "rot_dim": 8, "vdim": 16, "kv_rank": 32,
+                              "q_rank": 24, "scale": 0.3, "rot": {"base": 50.0, "dims": 4}}),
     ]
     W, eps = 80, 1e-5
     torch.manual_seed(8)
@@ -399,6 +402,40 @@ def test_long_decoding_and_reused_slots(name, folders):
     assert np.array_equal(first, again)
 
 
+def test_a_width_that_fits_no_tensor_core_product(tmp_path):
+    """Width 52 and inner sizes that are no multiples of 8: in bfloat16 every product takes
+    the CUDA-core kernel and the feed-forward's activation runs behind its product."""
+    import foundry_b200 as fb
+    from foundry_b200.weights.safetensors_io import SINGLE_FILE, save_file
+    doc = {"architecture": "Vonulorn", "vocab": 77, "width": 52, "norm": {"eps": 1e-5},
+           "residual_mult": 0.25,
+           "layers": [
+               {"type": "delta", "mixer": {"heads": 2, "kv_heads": 2, "dim": 12, "vdim": 10, "conv": 3},
+                "mlp": {"kind": "dense", "ff": 90}},
+               {"type": "attention",
+                "mixer": {"heads": 3, "kv_heads": 3, "dim": 10, "vdim": 14, "scale": 0.3,
+                          "softcap": 3.0, "diff": 0.2, "q_temp": {"coef": 0.4, "every": 3}},
+                "mlp": {"kind": "dense", "ff": 44}},
+               {"type": "latent_attention",
+                "mixer": {"heads": 2, "dim": 10, "rot_dim": 6, "vdim": 14, "kv_rank": 18, "q_rank": 20,
+                          "scale": 0.25, "rot": {"base": 777.0, "dims": 6}}, "mlp": None}]}
+    gen = torch.Generator().manual_seed(31)
+    weights = {k: tiny.draw(k, shape, gen) for k, shape in tiny.tensor_shapes(doc).items()}
+    folder = tmp_path / "odd"
+    folder.mkdir()
+    save_file({k: v.to(torch.bfloat16) for k, v in weights.items()}, str(folder / SINGLE_FILE),
+              metadata={"format": "pt"})
+    (folder / "config.json").write_text(json.dumps(doc))
+    rng = np.random.default_rng(3)
+    prompts = [[int(t) for t in rng.integers(0, 77, n)] for n in (70, 9)]
+    want = [plain.forward(doc, double(weights), p).numpy() for p in prompts]
+    for dtype in ("float32", "bfloat16"):
+        engine = fb.Engine.from_folder(str(folder), dtype=dtype, max_tokens=512, max_slots=3)
+        got = run_cutting(engine, prompts, [[66, 2, 1, 1], [5, 1, 2, 1]])
+        for g, w in zip(got, want):
+            assert rel_error(g, w) < bound(dtype, 2.0), dtype
+
+
 def greedy(cfg, weights, prompt, count):
     tokens = list(prompt)
     for _ in range(count):
@@ -463,3 +500,17 @@ def test_trace_replay_and_command_line(folders, tmp_path):
     assert run.returncode == 0, run.stderr[-2000:]
     want = greedy(cfg, double(weights), a, 4)
     assert json.loads(run.stdout.strip().split("\n")[-1]) == want
+
+
+def test_command_line_bench_on_a_vonulorn_folder(folders, tmp_path):
+    """`foundry bench` (prompt step, decode steps, report with bytes and operations)
+    on a model with state rows, latent rows and two-map attention."""
+    folder, _ = folders["mixed"]
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "foundry"), "bench", "--model",
+                           folder, "--prompt-tokens", "20", "--new-tokens", "5", "--runs", "2",
+                           "--batch-size", "3", "--out", str(tmp_path)],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    report = json.loads((tmp_path / "report.json").read_text())
+    assert len(report["runs"]) == 2 and all(len(r) == 5 for r in report["runs"][0]["token_ids"])
+    assert report["runs"][0]["token_ids"] == report["runs"][1]["token_ids"]
