@@ -97,7 +97,7 @@ struct RowScale {
   int count, stride;
   float inv_dim, eps;
 };
-// Residual sink (epilogue 3): resid[t, n] += out[t, n]; xg[t, n] = bf16(resid * gamma[n]);
+// Residual sink (epilogue 3): resid[t, n] += scale * out[t, n]; xg[t, n] = bf16(resid * gamma[n]);
 // ss_out[blockIdx.x * ss_stride + t] = this CTA's sum over its rows of resid^2.
 struct ResidualSink {
   float* resid;
@@ -107,6 +107,7 @@ struct ResidualSink {
   long long ldxg;
   float* ss_out;
   int ss_stride;
+  float scale;  // the constant on the product before it joins the residual (1: none)
 };
 template <bool ROPE> struct RopeArg { using type = NoRope; };
 template <> struct RopeArg<true> { using type = RopeWrite; };
@@ -417,7 +418,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
         if (live) {
 #pragma unroll
           for (int wi = 0; wi < WARPS; ++wi) v += red[wi][row][tok];
-          v = old_resid[it] + v * row_scale(tok);
+          v = old_resid[it] + sink.scale * (v * row_scale(tok));
           sink.resid[(size_t)tok * sink.ldr + n0 + row] = v;
           sink.xg[(size_t)tok * sink.ldxg + n0 + row] = __float2bfloat16_rn(v * gamma[it]);
         }
@@ -582,9 +583,9 @@ FB_API int fb_gemm_skinny(const void* x, long long ldx, const void* w, long long
 FB_API int fb_gemm_skinny_residual(const void* x, long long ldx, const void* w, long long ldw,
                                    int T, int N, int K, float* resid, long long ldr,
                                    const float* gamma, void* xg, long long ldxg, float* ss_out,
-                                   int ss_stride, const void* next, long long next_bytes,
-                                   int warps, cudaStream_t stream) {
-  ResidualSink sink{resid, ldr, gamma, (__nv_bfloat16*)xg, ldxg, ss_out, ss_stride};
+                                   int ss_stride, float scale, const void* next,
+                                   long long next_bytes, int warps, cudaStream_t stream) {
+  ResidualSink sink{resid, ldr, gamma, (__nv_bfloat16*)xg, ldxg, ss_out, ss_stride, scale};
   return launch_skinny(x, ldx, w, ldw, resid, ldr, 1, T, N, K, 3, next, next_bytes, 1, 0, warps,
                        1, RopeWrite{}, RowScale{}, sink, stream);
 }

@@ -58,8 +58,8 @@ _SIGNATURES = {
                        c_int, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p, c_int, c_int, c_int,
                        c_float, c_void_p],
     "fb_gemm_skinny_residual": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_void_p,
-                                c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_ll,
-                                c_int, c_void_p],
+                                c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_float, c_void_p,
+                                c_ll, c_int, c_void_p],
     "fb_apply_row_scale": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
                            c_ll, c_int, c_int, c_void_p],
     "fb_gemm_skinny_rope": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p,
@@ -313,10 +313,13 @@ class Planes:
 class ResidualSink:
     """What a part's last projection may do instead of returning its result:
     add it to the float32 residual rows `resid` and prepare the input of the
-    norm with weight `gamma` and `eps` that follows (see `gemm_bf16`)."""
+    norm with weight `gamma` and `eps` that follows (see `gemm_bf16`). `scale`:
+    the result joins the residual times this constant (a block that scales its
+    parts' outputs sets it; only the weight-streaming product takes another
+    value than 1)."""
 
-    def __init__(self, resid: torch.Tensor, gamma: torch.Tensor, eps: float):
-        self.resid, self.gamma, self.eps = resid, gamma, float(eps)
+    def __init__(self, resid: torch.Tensor, gamma: torch.Tensor, eps: float, scale: float = 1.0):
+        self.resid, self.gamma, self.eps, self.scale = resid, gamma, float(eps), float(scale)
 
 
 class RowScaled:
@@ -784,7 +787,8 @@ def gemm_skinny_residual(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink,
           _dev(w, "w", contiguous=False), _rows(w, "w"), M, N, K,
           _dev(resid, "resid", torch.float32, contiguous=False), _rows(resid, "resid"),
           _dev(sink.gamma, "gamma", torch.float32), values.data_ptr(), N, shares.data_ptr(), 16,
-          *_prefetch_range(then_reads), warps, _stream(), tag=("m{} k{} n{}", M, K, N))
+          float(sink.scale), *_prefetch_range(then_reads), warps, _stream(),
+          tag=("m{} k{} n{}", M, K, N))
     return NormPending(sink, values, shares)
 
 
@@ -1270,7 +1274,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         return gemm_skinny(x, w, out, then_reads=then_reads, warps=warps)
     if rows_usable(x, w) and (out is None or out.stride(1) == 1):
-        if (residual is not None and NORM_FUSION and out is None
+        if (residual is not None and NORM_FUSION and out is None and residual.scale == 1.0
                 and tuple(residual.resid.shape) == (M, N) and not isinstance(x, RowScaled)):
             return gemm_rows_residual(x, w, residual)
         return gemm_rows(x, w, out, out_dtype)
@@ -1281,6 +1285,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         # applies a deferred row scale, and in front of a norm adds into the residual
         bn, form = prompt_plan(M, N) if many else (128, 0)
         if (residual is not None and NORM_FUSION and M <= NORM_FUSION_ROWS and out is None
+                and residual.scale == 1.0
                 and tuple(residual.resid.shape) == (M, N) and not isinstance(x, RowScaled)):
             values = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)
             shares = torch.empty(((N + bn - 1) // bn, (M + 31) // 32 * 32), dtype=torch.float32,

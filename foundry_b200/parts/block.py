@@ -219,16 +219,33 @@ class ScaledPreNormBlock(Part):
     def first_weight(self):
         return first_weight_of(self.mixer)
 
-    def forward(self, ctx, resid: torch.Tensor, delta, cache):
+    def input_sink(self, resid: torch.Tensor):
+        """The sink of this block's first norm, if its mixer takes the norm's
+        output without its row scale; for whatever runs in front of the block."""
+        return _sink_for(self.mixer_norm, self.mixer, resid)
+
+    def _scaled(self, sink):
+        """The sink with this block's constant: the product that uses it adds m times its result."""
+        if sink is not None:
+            sink.scale = self.residual_scale
+        return sink
+
+    def _leaves(self, y):
+        """A part's output on its way to the residual: already summed by the part's last
+        product (`ops.NormPending`), or still to be added times the constant."""
         from ..kernels import ops
+        return y if isinstance(y, ops.NormPending) else ops.ScaledDelta(y, self.residual_scale)
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache):
         after_block = getattr(ctx, "reads_after_part", None)
-        ctx.residual_sink = None  # a projection's own sum would miss the constant
+        sink_after_block = self._scaled(getattr(ctx, "residual_sink", None))
         normed = self.mixer_norm.add_norm(resid, delta)
-        ctx.reads_after_part = (first_weight_of(self.feed_forward) if self.feed_forward is not None
-                                else after_block)
-        mixed = ops.ScaledDelta(self.mixer.forward(ctx, normed, cache), self.residual_scale)
         if self.feed_forward is None:
-            return mixed
+            ctx.reads_after_part, ctx.residual_sink = after_block, sink_after_block
+            return self._leaves(self.mixer.forward(ctx, normed, cache))
+        ctx.reads_after_part = first_weight_of(self.feed_forward)
+        ctx.residual_sink = self._scaled(_sink_for(self.feed_forward_norm, self.feed_forward, resid))
+        mixed = self._leaves(self.mixer.forward(ctx, normed, cache))
         normed = self.feed_forward_norm.add_norm(resid, mixed)
-        ctx.reads_after_part = after_block
-        return ops.ScaledDelta(self.feed_forward.forward(ctx, normed), self.residual_scale)
+        ctx.reads_after_part, ctx.residual_sink = after_block, sink_after_block
+        return self._leaves(self.feed_forward.forward(ctx, normed))

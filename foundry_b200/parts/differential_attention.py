@@ -31,12 +31,13 @@ from ..kernels import ops
 from ..weights.loader import ExpectedTensor
 from .base import Fetch, Part, register_mixer
 from .linear import Linear
-from .products import product_f32
+from .products import product_f32, product_to_residual
 
 
 @register_mixer("differential_attention")
 class DifferentialAttention(Part):
     replay_safe = True
+    accepts_row_scaled = True  # the first product applies a deferred norm's row scale
 
     def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
                  eps: float, diff: float, softcap: float = 0.0, temp_coef: float = 0.0,
@@ -90,4 +91,4 @@ class DifferentialAttention(Part):
         ops.attention_sink(ctx, q, attn, table, cache.k, cache.v, self.heads, self.kv_heads,
                            self.dim, self.vdim, self.scale, softcap=self.softcap, maps=2,
                            combine=(self.lam, self.eps, 1.0 - self.diff))
-        return product_f32(attn, self.o.weight)
+        return product_to_residual(ctx, attn, self.o.weight)

@@ -39,12 +39,13 @@ from ..kernels import ops
 from ..weights.loader import ExpectedTensor
 from .base import Fetch, Part, register_mixer
 from .linear import matmul_nt
-from .products import product_f32
+from .products import product_f32, product_to_residual
 
 
 @register_mixer("latent_attention")
 class LatentAttention(Part):
     replay_safe = True
+    accepts_row_scaled = True  # the first product applies a deferred norm's row scale
 
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
                  q_rank: int, scale: float, eps: float, rot_base: float,
@@ -127,7 +128,7 @@ class LatentAttention(Part):
             ops.attention_maps_rows(ctx, q_full.view(T, H * (d + c)), out, kv[:, :, :d],
                                     rows[:, r:], kv[:, :, d:], H, d + c, e, self.scale,
                                     sink_logits=self.sink_logits)
-            return product_f32(out, self.o)
+            return product_to_residual(ctx, out, self.o)
         q_plain = torch.empty((T, H * d), **act)
         q_wide = torch.empty((T, H, self.row), **act)
         ops.split_rotate(q, q_plain, q_wide, r, self.freq, self.rot_dims, ctx.positions,
@@ -139,4 +140,4 @@ class LatentAttention(Part):
                            values_in_keys=True)
         out = torch.empty((T, H, e), **act)
         ops.head_products(mixed.view(T, H, r), self.uv, out)
-        return product_f32(out.view(T, H * e), self.o)
+        return product_to_residual(ctx, out.view(T, H * e), self.o)

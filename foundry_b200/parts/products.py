@@ -18,6 +18,18 @@ def product_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if x.shape[0] == 0:
         return out
     if x.dtype == torch.float32 or x.shape[1] < SMALL_K:
-        return ops.gemm_simt(x, w, out)
+        return ops.gemm_simt(ops.plain(x), w, out)
     y = matmul_nt(x, w, out)
     return y if isinstance(y, torch.Tensor) else out
+
+
+def product_to_residual(ctx, x: torch.Tensor, w: torch.Tensor):
+    """A part's last product, whose result joins the residual: float32 as
+    `product_f32` gives it, or, where the block offers the next norm's sink
+    (`ctx.residual_sink`, single-token steps in bfloat16), the sum and the norm's
+    preparation made in the product's epilogue (an `ops.NormPending` comes back)."""
+    sink = getattr(ctx, "residual_sink", None)
+    if sink is None or x.dtype == torch.float32 or x.shape[1] < SMALL_K or x.shape[0] == 0:
+        return product_f32(x, w)
+    return matmul_nt(x, w, out_dtype=torch.float32, residual=sink,
+                     then_reads=getattr(ctx, "reads_after_part", None))

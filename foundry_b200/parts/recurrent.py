@@ -43,7 +43,7 @@ from ..cache.store import StateRequest, StateView
 from ..kernels import ops
 from ..weights.loader import ExpectedTensor
 from .base import Fetch, Part, register_mixer
-from .products import product_f32
+from .products import product_f32, product_to_residual
 
 
 def _f32(t: torch.Tensor) -> torch.Tensor:
@@ -122,6 +122,7 @@ class GatedDelta(Part):
     output gate's activation and the constant inside the unit vectors' root are
     parameters."""
     replay_safe = True
+    accepts_row_scaled = True  # the first product applies a deferred norm's row scale
 
     def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int,
                  eps: float, unit_eps: float = 1e-6, gate: str = "silu", *,
@@ -180,7 +181,7 @@ class GatedDelta(Part):
                        "S", o, H, H // G, d, v, beta=p[:, at:at + H], decay_per_head=True)
         y = torch.empty((T, H * v), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, self.norm, False, p[:, C:at], self.gate, self.eps, y, H, v)
-        return product_f32(y, self.o)
+        return product_to_residual(ctx, y, self.o)
 
 
 @register_mixer("wkv_time_mix")
