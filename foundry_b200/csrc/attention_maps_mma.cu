@@ -328,6 +328,205 @@ __global__ void __launch_bounds__(THREADS) attn_maps_kernel(const MapsParams p) 
   }
 }
 
+// ------------------------------------------------- heads as rows over shared key rows
+// Attention of ALL query heads over one key row per token whose first DV_ALL elements are
+// also the value (the folded form of a latent attention: query rows of KW = DV_ALL + rotated
+// elements). The 64 rows of a block are consecutive (token, head) pairs of one sequence, so a
+// token's heads share every key tile: row R of the sequence's rows is head R % H of its token
+// R / H, at that token's position. A block makes DVC of the value columns (blockIdx.y picks
+// which), and with `splits` > 1 walks only its share of the pages and leaves (max, sum,
+// weighted values) for the merge kernel of csrc/sink_attention.cu (natural-log maxima), which
+// also adds the sink; unsplit, the sink is the start of the running maximum and sum.
+// The query fragments are read from shared memory at every k-step (a block's registers hold
+// the 64 x DVC output), the key tile's pitch P is KW rounded up to 64 elements.
+struct FoldedParams {
+  const __nv_bfloat16* q;    // [rows, KW]: row (token * H + head)
+  __nv_bfloat16* out;        // [rows, DV_ALL]
+  float* partial;            // [rows, splits, DV_ALL + 2] or null
+  const int* cu_tokens; const int* kv_lens; const int* page_table; int max_pages;
+  const __nv_bfloat16* k; long long k_page;   // the cache: [pages, 1, 64, KW]
+  int n_seqs, H, KW, DV_ALL, splits;
+  float scale;
+  const float* sink_logit;   // [H] or null
+};
+
+template <int P, int DVC>
+__global__ void __launch_bounds__(THREADS) attn_folded_kernel(const FoldedParams p) {
+  fb_pdl_wait();
+  constexpr int NT = DVC / 8;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
+  __nv_bfloat16* sK = sQ + 64 * P;  // [2][64][P]
+  __shared__ int s_info[2];
+  if (threadIdx.x == 0) {
+    int b = (int)(gridDim.x - 1 - blockIdx.x), s = 0;
+    for (; s < p.n_seqs; ++s) {
+      const int nb = ((p.cu_tokens[s + 1] - p.cu_tokens[s]) * p.H + 63) / 64;
+      if (b < nb) break;
+      b -= nb;
+    }
+    s_info[0] = s < p.n_seqs ? s : -1;
+    s_info[1] = b;
+  }
+  __syncthreads();
+  const int seq = s_info[0];
+  if (seq < 0) return;
+  const int H = p.H, KW = p.KW;
+  const int row0 = s_info[1] * 64;
+  const int tok0 = p.cu_tokens[seq], q_len = p.cu_tokens[seq + 1] - tok0;
+  const int kv_len = p.kv_lens[seq];
+  const int pos_first = kv_len - q_len;
+  const int rows_valid = min(64, q_len * H - row0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int vcol0 = blockIdx.y * DVC;
+  const int last_pos = pos_first + (row0 + rows_valid - 1) / H;
+  const int n_pages = last_pos / FB_PAGE + 1;
+  const int pg0 = (int)((long long)n_pages * blockIdx.z / p.splits);
+  const int pg1 = (int)((long long)n_pages * (blockIdx.z + 1) / p.splits);
+  const int* pages = p.page_table + (size_t)seq * p.max_pages;
+  const long long grow0 = (long long)tok0 * H + row0;  // the block's first row among all rows
+
+  load_cols<P>(sQ, p.q + grow0 * KW, KW, 64, rows_valid, KW, 0);
+  if (pg0 < pg1) load_cols<P>(sK, p.k + (long long)pages[pg0] * p.k_page, KW, 64, 64, KW, 0);
+  cp_async_commit();
+
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m[2], l[2];
+  int qpos[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = row0 + warp * 16 + g + r * 8;
+    qpos[r] = pos_first + row / H;
+    const bool own_sink = p.sink_logit != nullptr && p.splits == 1;
+    m[r] = own_sink ? p.sink_logit[row % H] * LOG2E : -INFINITY;
+    l[r] = own_sink ? 1.f : 0.f;
+  }
+  const float scale2 = p.scale * LOG2E;
+  const int first_pos_warp = pos_first + (row0 + warp * 16) / H;
+  const int last_pos_warp = pos_first + (row0 + warp * 16 + 15) / H;
+
+  for (int pg = pg0; pg < pg1; ++pg) {
+    const int st = (pg - pg0) & 1;
+    if (pg + 1 < pg1)
+      load_cols<P>(sK + (st ^ 1) * 64 * P, p.k + (long long)pages[pg + 1] * p.k_page, KW, 64, 64, KW, 0);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int key0 = pg * FB_PAGE;
+    if (key0 <= last_pos_warp) {
+      const __nv_bfloat16* tK = sK + st * 64 * P;
+      float s[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int k = 0; k < KW / 16; ++k) {
+        uint32_t qf[4];
+        ldsm_x4(qf, smem_u32(sQ + Swz<P>::off(warp * 16 + (lane & 15), k * 16 + (lane >> 4) * 8)));
+#pragma unroll
+        for (int n2 = 0; n2 < 4; ++n2) {
+          uint32_t b[4];
+          ldsm_x4(b, smem_u32(tK + Swz<P>::off(n2 * 16 + (lane & 7) + (lane >> 4) * 8,
+                                                k * 16 + ((lane >> 3) & 1) * 8)));
+          mma_bf16(s[2 * n2], qf, b[0], b[1]);
+          mma_bf16(s[2 * n2 + 1], qf, b[2], b[3]);
+        }
+      }
+      const bool need_mask = key0 + FB_PAGE - 1 > first_pos_warp;
+      float mx[2] = {m[0], m[1]};
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[n][e] * scale2;
+          if (need_mask && key0 + n * 8 + 2 * t + (e & 1) > qpos[e >> 1]) v = -INFINITY;
+          s[n][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+      float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        corr[r] = exp2f(m[r] - mx[r]);
+        if (mx[r] == -INFINITY) { corr[r] = 1.f; mx[r] = 0.f; }  // nothing seen yet
+      }
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = exp2f(s[n][e] - mx[e >> 1]);
+          s[n][e] = pv;
+          sum[e >> 1] += pv;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        l[r] = l[r] * corr[r] + sum[r];
+        m[r] = (sum[r] == 0.f && l[r] == 0.f) ? -INFINITY : mx[r];
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int n2 = 0; n2 < NT / 2; ++n2) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, smem_u32(tK + Swz<P>::off(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                                    vcol0 + n2 * 16 + (lane >> 4) * 8)));
+          mma_bf16(o[2 * n2], a, b[0], b[1]);
+          mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();  // (a block without pages has only asked for its queries)
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + g + r * 8;
+    if (row >= rows_valid) continue;
+    if (p.splits > 1) {
+      float* dst = p.partial + ((grow0 + row) * p.splits + blockIdx.z) * (p.DV_ALL + 2);
+      if (t == 0 && blockIdx.y == 0) { dst[0] = m[r] / LOG2E; dst[1] = l[r]; }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        dst[2 + vcol0 + n * 8 + 2 * t] = o[n][2 * r];
+        dst[2 + vcol0 + n * 8 + 2 * t + 1] = o[n][2 * r + 1];
+      }
+    } else {
+      const float inv = 1.0f / l[r];
+      __nv_bfloat16* dst = p.out + (grow0 + row) * p.DV_ALL + vcol0;
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+        *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = pack_bf16(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+    }
+  }
+}
+
+template <int P, int DVC>
+int launch_folded(const FoldedParams& p, int q_blocks, cudaStream_t stream) {
+  const size_t smem = (size_t)3 * 64 * P * sizeof(__nv_bfloat16);
+  static bool seen[64];
+  if (smem > 48 * 1024 && fb_first_use_on_device(seen))
+    cudaFuncSetAttribute(attn_folded_kernel<P, DVC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  fb_launch(attn_folded_kernel<P, DVC>, dim3(q_blocks, p.DV_ALL / DVC, p.splits), dim3(THREADS), smem,
+            stream, p);
+  return fb_check_launch("attention_folded");
+}
+
 template <int DK, int DV, int MAPS>
 int launch_maps(const MapsParams& p, int q_blocks, cudaStream_t stream) {
   constexpr int PK = pitch_of(MAPS * DK), PV = pitch_of(DV);
@@ -380,4 +579,26 @@ FB_API int fb_attention_maps(const void* q, long long q_stride, void* out, long 
   FB_MAPS(48, 16, 1); FB_MAPS(48, 32, 1); FB_MAPS(80, 64, 1); FB_MAPS(96, 64, 1); FB_MAPS(192, 128, 1);
 #undef FB_MAPS
   return fb_fail(1, "attention_maps: no kernel");
+}
+
+// The folded latent attention on the tensor cores (see `attn_folded_kernel`). KW and DV:
+// (144, 128), (288, 256), (576, 512). `partial` with splits > 1; the caller then runs the merge.
+FB_API int fb_attention_folded(const void* q, void* out, float* partial, const int* cu_tokens,
+                               const int* kv_lens, const int* page_table, int max_pages,
+                               const void* k_cache, long long k_page, int n_seqs, int q_blocks,
+                               int H, int KW, int DV, int splits, float scale,
+                               const float* sink_logit, cudaStream_t stream) {
+  FB_REQUIRE(n_seqs >= 0 && q_blocks >= 0 && H > 0 && splits >= 1 && splits <= 64 &&
+             (splits == 1 || partial != nullptr), "attention_folded: bad sizes");
+  FB_REQUIRE((KW == 144 && DV == 128) || (KW == 288 && DV == 256) || (KW == 576 && DV == 512),
+             "attention_folded: no kernel for key rows of %d with values of %d", KW, DV);
+  FB_REQUIRE(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)out) % 16 == 0 && k_page % 8 == 0 &&
+             page_table != nullptr && max_pages > 0, "attention_folded: rows must start on 16-byte boundaries");
+  if (n_seqs == 0 || q_blocks == 0) return 0;
+  FoldedParams p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, cu_tokens, kv_lens, page_table,
+                 max_pages, (const __nv_bfloat16*)k_cache, k_page, n_seqs, H, KW, DV, splits, scale,
+                 sink_logit};
+  if (KW == 144) return launch_folded<192, 128>(p, q_blocks, stream);
+  if (KW == 288) return launch_folded<320, 256>(p, q_blocks, stream);
+  return launch_folded<576, 256>(p, q_blocks, stream);
 }

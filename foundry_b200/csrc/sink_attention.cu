@@ -939,3 +939,24 @@ FB_API int fb_attention_sink(const void* q, long long q_stride, void* out, long 
   }
   return fb_check_launch("attention_sink");
 }
+
+// The merge alone, for a kernel of another file that leaves the same records: partial
+// [T * H, splits, VD + 2] of (max, sum, weighted values), one map; bfloat16 or float32 out.
+FB_API int fb_attention_sink_merge(const float* partial, void* out, long long out_stride, int dtype,
+                                   const int* seq_of_token, int T, int H, int VD, int splits,
+                                   const float* sink_logit, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && H > 0 && VD > 0 && VD <= 768 && splits >= 1 && splits <= 64 && partial != nullptr,
+             "attention_sink_merge: bad sizes");
+  if (T == 0) return 0;
+  ScoreRule rule{0, 0, sink_logit != nullptr ? 2 : 0, sink_logit, 1.f, 0.f, 0.f, 0.f, 0.f, 1.f};
+  if (VD > 256) {
+    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_merge_kernel<E, 1, 24>,
+        dim3(T, (H + WARPS - 1) / WARPS), dim3(WARPS * 32), 0, stream, partial, (E*)out, out_stride,
+        seq_of_token, H, VD, splits, rule)));
+  } else {
+    FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_sink_merge_kernel<E, 1, 8>,
+        dim3(T, (H + WARPS - 1) / WARPS), dim3(WARPS * 32), 0, stream, partial, (E*)out, out_stride,
+        seq_of_token, H, VD, splits, rule)));
+  }
+  return fb_check_launch("attention_sink_merge");
+}

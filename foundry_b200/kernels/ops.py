@@ -108,6 +108,11 @@ _SIGNATURES = {
                        c_int, c_int, c_int, c_int, c_void_p],
     "fb_split_rotate": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "fb_attention_folded": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                            c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                            c_void_p, c_void_p],
+    "fb_attention_sink_merge": [c_void_p, c_void_p, c_ll, c_int, c_void_p, c_int, c_int, c_int,
+                                c_int, c_void_p, c_void_p],
     "fb_attention_maps": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -1842,6 +1847,55 @@ def attention_maps_fits(ctx, q: torch.Tensor, dim: int, vdim: int, maps: int) ->
     """Whether the step is a prompt step in bfloat16 of sizes the tensor-core kernel has."""
     return (MAPS_ATTENTION_TC and not ctx.is_decode and q.dtype == torch.bfloat16
             and (dim, vdim) in MAPS_TC_SIZES.get(maps, ()))
+
+
+# (key row, value) sizes of the tensor-core kernel for latent rows with all heads as rows
+FOLDED_TC_SIZES = {(144, 128), (288, 256), (576, 512)}
+FOLDED_CTAS = 296  # blocks a single-token step's attention should come to (two an SM)
+
+
+def attention_folded_fits(q: torch.Tensor, row: int, vdim: int) -> bool:
+    return MAPS_ATTENTION_TC and q.dtype == torch.bfloat16 and (row, vdim) in FOLDED_TC_SIZES
+
+
+def attention_folded(ctx, q: torch.Tensor, out: torch.Tensor, page_table, cache: torch.Tensor,
+                     H: int, row: int, vdim: int, scale: float,
+                     sink_logits: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of all heads over one cached row per token whose first `vdim` elements
+    are the value (csrc/attention_maps_mma.cu, `attn_folded_kernel`): q [T, H * row], out
+    [T, H * vdim], cache [pages, 1, PAGE, row], bfloat16. Any step: single tokens (the
+    pages are shared among blocks and merged), prompts and portions that continue one."""
+    T = q.shape[0]
+    _check_kv_pair(cache, cache, 1, row, row, torch.bfloat16)
+    if tuple(q.shape) != (T, H * row) or tuple(out.shape) != (T, H * vdim) \
+            or not q.is_contiguous() or not out.is_contiguous():
+        raise KernelError("attention_folded: q and out are contiguous [T, H * row], [T, H * vdim]")
+    if ctx.is_decode:
+        q_blocks = ctx.n_seqs * ((H + 63) // 64)
+    elif ctx.query_blocks_bound is not None:
+        q_blocks = (ctx.n_tokens * H + 63) // 64 + ctx.n_seqs
+    else:
+        cu = ctx.cu_tokens_host
+        q_blocks = sum(((cu[i + 1] - cu[i]) * H + 63) // 64 for i in range(ctx.n_seqs))
+    splits, partial = 1, None
+    if ctx.is_decode and T > 0:
+        halves = max(1, vdim // 256)
+        splits = max(1, min((ctx.max_kv_len + PAGE - 1) // PAGE, 64,
+                            FOLDED_CTAS // max(1, q_blocks * halves)))
+        if splits > 1:
+            partial = torch.empty(T * H * splits * (vdim + 2), dtype=torch.float32, device=q.device)
+    _call("fb_attention_folded", _dev(q, "q", torch.bfloat16), _dev(out, "out", torch.bfloat16),
+          0 if partial is None else partial.data_ptr(), _dev(ctx.cu_tokens, "cu_tokens", torch.int32),
+          _dev(ctx.kv_lens, "kv_lens", torch.int32), _dev(page_table, "page_table", torch.int32),
+          page_table.shape[1], cache.data_ptr(), cache.stride(0), ctx.n_seqs, q_blocks, H, row, vdim,
+          splits, float(scale),
+          0 if sink_logits is None else _dev(sink_logits, "sink_logits", torch.float32), _stream())
+    if splits > 1:
+        _call("fb_attention_sink_merge", partial.data_ptr(), _dev(out, "out"), out.stride(0),
+              code_of(out.dtype), _dev(ctx.seq_of_token, "seq_of_token", torch.int32), T, H, vdim,
+              splits, 0 if sink_logits is None else _dev(sink_logits, "sink_logits", torch.float32),
+              _stream())
+    return out
 
 
 def attention_maps_paged(ctx, q, out, page_table, k_cache, v_cache, H: int, G: int, dim: int,

@@ -135,9 +135,14 @@ class LatentAttention(Part):
                          ctx.seq_of_token, H, d, c)
         ops.head_products(q_plain.view(T, H, d), self.uk_t, q_wide[:, :, :r])
         mixed = torch.empty((T, H * r), **act)
-        ops.attention_sink(ctx, q_wide.view(T, H * self.row), mixed, table, cache.k, cache.k, H, 1,
-                           self.row, r, self.scale, sink_logits=self.sink_logits,
-                           values_in_keys=True)
+        if ops.attention_folded_fits(q_wide, self.row, r):
+            # all heads as the rows of tensor-core tiles over the shared latent rows
+            ops.attention_folded(ctx, q_wide.view(T, H * self.row), mixed, table, cache.k, H,
+                                 self.row, r, self.scale, sink_logits=self.sink_logits)
+        else:
+            ops.attention_sink(ctx, q_wide.view(T, H * self.row), mixed, table, cache.k, cache.k, H,
+                               1, self.row, r, self.scale, sink_logits=self.sink_logits,
+                               values_in_keys=True)
         out = torch.empty((T, H, e), **act)
         ops.head_products(mixed.view(T, H, r), self.uv, out)
         return product_to_residual(ctx, out.view(T, H * e), self.o)

@@ -127,6 +127,14 @@ def test_mixers_at_other_sizes(dtype):
                        "softcap": 30.0, "diff": 0.6, "q_temp": {"coef": 0.3, "every": 64}}),
         ("delta", {"heads": 6, "kv_heads": 2, "dim": 8, "vdim": 72, "conv": 5}),
         ("delta", {"heads": 1, "kv_heads": 1, "dim": 128, "vdim": 64, "conv": 1}),
+        # latent rows of 128 + 16, 256 + 32 and 512 + 64: in bfloat16 the heads-as-rows
+        # tensor-core kernel (five heads: a block's 64 rows span 13 tokens)
+        ("latent_attention", {"heads": 5, "dim": 16, "rot_dim": 16, "vdim": 24, "kv_rank": 128,
+                              "q_rank": 40, "scale": 0.1, "rot": {"base": 10000.0, "dims": 16}}),
+        ("latent_attention", {"heads": 3, "dim": 8, "rot_dim": 32, "vdim": 8, "kv_rank": 256,
+                              "q_rank": 32, "scale": 0.07, "rot": {"base": 10000.0, "dims": 32}}),
+        ("latent_attention", {"heads": 2, "dim": 8, "rot_dim": 64, "vdim": 16, "kv_rank": 512,
+                              "q_rank": 32, "scale": 0.05, "rot": {"base": 1000.0, "dims": 64}}),
         # fewer rotated elements than the rotated part holds: the rest passes unchanged
         ("latent_attention", {"heads": 2, "dim": 16, "rot_dim": 8, "vdim": 16, "kv_rank": 32,
                               "q_rank": 24, "scale": 0.3, "rot": {"base": 50.0, "dims": 4}}),
@@ -215,29 +223,31 @@ def crafted_differential(W, d=4, e=4):
                "a.lq2": z, "a.lk2": z}
 
 
-def crafted_latent(W, d=4, c=4, e=4):
+def crafted_latent(W, d=4, c=4, e=4, r=8):
     """The query reads input 1 through its latent, the key input 2 of the cached latent,
     values the latent's elements 4..8; the rotated parts are idle in the scores (their
     query rows are zero) but are written and read all the same."""
-    m = {"heads": 1, "dim": d, "rot_dim": c, "vdim": e, "kv_rank": 8, "q_rank": W, "scale": 5.0,
-         "rot": {"base": 100.0, "dims": c}}
+    # (only 8 of the latent's r elements are fed: the norm over all r makes them
+    # sqrt(r / 8) larger, which the scale takes back)
+    m = {"heads": 1, "dim": d, "rot_dim": c, "vdim": e, "kv_rank": r, "q_rank": W,
+         "scale": 5.0 * (8.0 / r) ** 0.5, "rot": {"base": 100.0, "dims": c}}
     uq = torch.zeros(d + c, W)
     uq[0, 1] = 1.0
-    dkv = torch.zeros(8 + c, W)
+    dkv = torch.zeros(r + c, W)
     dkv[:8, :8] = torch.eye(8)
-    dkv[8:, 8:8 + c] = torch.eye(c)
-    uk, uv = torch.zeros(d, 8), torch.zeros(e, 8)
+    dkv[r:, 8:8 + c] = torch.eye(c)
+    uk, uv = torch.zeros(d, r), torch.zeros(e, r)
     uk[0, 2] = 1.0
-    uv[:4, 4:] = torch.eye(4)
+    uv[:4, 4:8] = torch.eye(4)
     out = torch.zeros(W, e)
     out[:4, :4] = torch.eye(4)
     return m, {"a.dq": torch.eye(W), "a.dq.norm": torch.ones(W), "a.uq": uq, "a.dkv": dkv,
-               "a.dkv.norm": torch.ones(8), "a.uk": uk, "a.uv": uv, "a.sink": torch.tensor([2.0]),
+               "a.dkv.norm": torch.ones(r), "a.uk": uk, "a.uv": uv, "a.sink": torch.tensor([2.0]),
                "a.o": out}
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("sizes", ["small", "tensor-core"])
+@pytest.mark.parametrize("sizes", ["small", "tensor-core", "folded"])
 @pytest.mark.parametrize("kind", ["attention", "latent_attention"])
 def test_one_key_that_stands_out_is_found_wherever_it_lies(kind, sizes, dtype):
     """Crafted mixers in which one key dominates one query: at the first tokens, on both
@@ -246,8 +256,12 @@ def test_one_key_that_stands_out_is_found_wherever_it_lies(kind, sizes, dtype):
     sizes whose prompts run on the tensor cores in bfloat16."""
     from foundry_b200.cache import SequenceCache
     W = 32
+    if kind == "attention" and sizes == "folded":
+        pytest.skip("the latent attention's kernel")
     if kind == "attention":
         m, weights = crafted_differential(W) if sizes == "small" else crafted_differential(W, 16, 32)
+    elif sizes == "folded":  # latent rows of 128 + 16: every bfloat16 step on the heads-as-rows kernel
+        m, weights = crafted_latent(W, 8, 16, 24, 128)
     else:
         m, weights = crafted_latent(W) if sizes == "small" else crafted_latent(W, 32, 16, 16)
     part = mixer_part(kind, m, W, 1e-6, weights, dtype)
