@@ -58,15 +58,15 @@ def _vonulorn(layers, width, heads, kv_heads, dim, ff, vocab, kv_rank, q_rank, t
         elif kind == "attention":
             each = min(dim, 64)  # a map's key size; as many heads as keep the projections' sizes
             mixer = {"heads": heads * dim // (2 * each), "kv_heads": max(1, kv_heads * dim // (2 * each)),
-                     "dim": each, "vdim": 2 * each, "scale": each ** -0.5, "softcap": 30.0,
-                     "diff": 0.6, "q_temp": {"coef": 0.3, "every": 64}}
+                     "dim": each, "vdim": 2 * each, "scale": each ** -0.5, "softcap": 50.0,
+                     "diff": 0.8, "q_temp": {"coef": 0.2, "every": 128}}
         else:
             mixer = {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim,
                      "kv_rank": kv_rank, "q_rank": q_rank, "scale": (dim + dim // 2) ** -0.5,
-                     "rot": {"base": 1000000.0, "dims": dim // 2}}
+                     "rot": {"base": 10000.0, "dims": dim // 2}}
         stack.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
-    return {"architecture": "Vonulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "residual_mult": 0.5, "layers": stack}
+    return {"architecture": "Vonulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "residual_mult": 0.7, "layers": stack}
 
 
 PRESETS: Dict[str, Dict] = {

@@ -33,16 +33,16 @@ CONFIGS = {
         ],
     },
     "other": {
-        "architecture": "Vonulorn", "vocab": 130, "width": 64, "norm": {"eps": 1e-6},
+        "architecture": "Vonulorn", "vocab": 130, "width": 64, "norm": {"eps": 3e-6},
         "residual_mult": 1.0,
         "layers": [
             {"type": "attention",
              "mixer": {"heads": 2, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.25,
-                       "softcap": 50.0, "diff": 0.8, "q_temp": {"coef": 0.5, "every": 70}},
+                       "softcap": 50.0, "diff": 0.25, "q_temp": {"coef": 0.5, "every": 70}},
              "mlp": None},
             {"type": "latent_attention",
              "mixer": {"heads": 1, "dim": 32, "rot_dim": 16, "vdim": 16, "kv_rank": 64, "q_rank": 24,
-                       "scale": 0.15, "rot": {"base": 1000000.0, "dims": 16}},
+                       "scale": 0.15, "rot": {"base": 500000.0, "dims": 16}},
              "mlp": {"kind": "dense", "ff": 100}},
             {"type": "delta",
              "mixer": {"heads": 3, "kv_heads": 1, "dim": 24, "vdim": 48, "conv": 3},
