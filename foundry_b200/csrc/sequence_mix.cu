@@ -1,7 +1,7 @@
 // Mixers that carry a state of fixed size from token to token: the pieces
 // around two linear recurrences over a per-head matrix state S [dim, vdim].
 //
-// Gated delta rule with a decay per key channel (one step, per head):
+// Gated delta rule with a decay per key channel, or one decay a head (one step, per head):
 //   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 // RWKV-style time mixing with a bonus for the current token (per head):
 //   o = (S + diag(b) k v^T)^T r;  S <- diag(w) S + k v^T

@@ -15,8 +15,20 @@
 // two caches have strides of their own. Positions are the tokens' own, so the
 // bias of a kept token is by the distance it really has.
 //
+// More rules of the same kernels, each off unless asked for (see `ScoreRule`): a cap
+// on the scores, softcap * tanh(s / softcap); a sink whose score is a learned number
+// per head instead of 0; two maps a head (two query vectors against two key vectors
+// side by side in a key row, two softmaxes over the same values, joined as
+// (a1 - lambda a2) / rms * scale in the kernel's epilogue); values that are the first
+// elements of the key rows (a cache of latent rows). Beside them the small kernels in
+// front of such attentions: queries times a temperature that grows with the position
+// plus the cache write; the norms and the rotation of a latent projection plus its
+// cache row; the split of query heads into a plain and a rotated part.
+//
 // This file holds the CUDA-core forms (32-bit arithmetic, any sizes): one warp
-// per (token, query head) walking the kept prefix and then the window.
+// per (token, query head) walking the kept prefix and then the window, either
+// straight from the cache or, for rows of whole 16-byte pieces, from a chunk's rows
+// staged in shared memory once for the heads that share a key head.
 #include "common.cuh"
 
 namespace {
