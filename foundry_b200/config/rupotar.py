@@ -22,6 +22,7 @@ from dataclasses import dataclass, field, replace
 from typing import Any, Dict, Mapping, Optional, Tuple
 
 from . import errors
+from .fields import need as _need, positive as _positive
 from .files import decode_json
 
 ARCHITECTURE = "Rupotar"
@@ -29,24 +30,6 @@ MIXER_TYPES = ("attention", "wkv", "channel_delta")
 # No key bounds the positions (the position vector is computed, not stored);
 # 2^24 keeps every position exactly representable in 32-bit floats.
 MAX_POSITIONS = 1 << 24
-
-
-def _need(doc: Mapping[str, Any], key: str, kind, where: str):
-    if key not in doc or doc[key] is None:
-        raise errors.ConfigJson(f"{where}: key {key!r} is missing")
-    value = doc[key]
-    if kind is float and isinstance(value, int) and not isinstance(value, bool):
-        value = float(value)
-    if not isinstance(value, kind) or isinstance(value, bool) and kind is not bool:
-        raise errors.ConfigJson(f"{where}: key {key!r} should be {kind.__name__}, found {value!r}")
-    return value
-
-
-def _positive(doc, key, where) -> int:
-    value = _need(doc, key, int, where)
-    if value <= 0:
-        raise errors.ConfigJson(f"{where}: {key} = {value} must be positive")
-    return value
 
 
 @dataclass(frozen=True)

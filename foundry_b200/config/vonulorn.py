@@ -19,8 +19,8 @@ from dataclasses import dataclass, field
 from typing import Any, Dict, Mapping, Optional, Tuple
 
 from . import errors
+from .fields import need as _need, positive as _positive
 from .files import decode_json
-from .rupotar import _need, _positive
 
 ARCHITECTURE = "Vonulorn"
 MIXER_TYPES = ("delta", "attention", "latent_attention")
